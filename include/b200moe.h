@@ -1,0 +1,158 @@
+/*
+ * b200moe - C ABI of the B200 (sm_100a) MoE-layer forward.
+ *
+ * One plan = one prepared MoE layer: fixed shapes, fixed device addresses,
+ * values may change in place between forwards. Nothing here allocates device
+ * memory, synchronises the device or reads device memory back to the host
+ * after b200moe_plan_bind(): b200moe_forward() only enqueues kernels on the
+ * given stream, so it can be captured into a CUDA graph.
+ *
+ * Each entry point names the interface of the reference project
+ * (llm-gpu-kernels, paths relative to its src/llm_gpu_kernels/) it replaces.
+ * All functions return 0 on success and a negative B200MOE_ERR_* code on
+ * failure; b200moe_last_error() gives the message for the calling thread.
+ * Nothing throws across this boundary.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* error codes */
+#define B200MOE_OK 0
+#define B200MOE_ERR_INVALID (-1)     /* bad argument / shape / alignment */
+#define B200MOE_ERR_CUDA (-2)        /* a CUDA runtime or driver call failed */
+#define B200MOE_ERR_UNSUPPORTED (-3) /* device is not sm_100, or schedule impossible for the shape */
+#define B200MOE_ERR_STATE (-4)       /* call order (forward before bind, ...) */
+
+/* device status word, bits as in the reference (moe.py:21-30, docs/MOE_USAGE.md:110-113) */
+#define B200MOE_STATUS_BAD_ID 1      /* an expert id outside [0,E) */
+#define B200MOE_STATUS_BAD_WEIGHT 2  /* a NaN/Inf routing weight */
+#define B200MOE_STATUS_TIMEOUT 4     /* a bounded wait inside a kernel gave up */
+#define B200MOE_STATUS_EP_OVERFLOW 8 /* expert-parallel receive capacity exceeded */
+
+/* weight formats */
+#define B200MOE_WEIGHTS_BF16 0
+#define B200MOE_WEIGHTS_W4G128 1 /* packed int4 (q+8), 8 per int32, BF16 scale per 128 along K */
+
+/* schedules (shape-only choice, the analogue of moe_full_policy.py:132-152) */
+#define B200MOE_SCHEDULE_AUTO 0
+#define B200MOE_SCHEDULE_GENERIC 1 /* CUDA-core tiles, any H/I */
+#define B200MOE_SCHEDULE_TCGEN05 2 /* TMA + tcgen05/TMEM tiles, needs H%8==0 and I%8==0 */
+
+typedef struct B200MoePlan B200MoePlan;
+
+/* Shape of one prepared layer. Replaces the shape arguments implied by
+ * prepare_moe(x, gate_up, down, ids, routing_weights) (moe.py:220-235). */
+typedef struct {
+  int32_t tokens;         /* T >= 0 */
+  int32_t experts;        /* 1 <= E <= 256 */
+  int32_t topk;           /* 1 <= K <= 32 */
+  int32_t hidden;         /* H > 0 */
+  int32_t intermediate;   /* I > 0 */
+  int32_t ids_are_int64;  /* 0: int32 ids, 1: int64 ids */
+  int32_t gate_up_format; /* B200MOE_WEIGHTS_* */
+  int32_t down_format;    /* B200MOE_WEIGHTS_* */
+  int32_t schedule;       /* B200MOE_SCHEDULE_* */
+  int32_t token_tile;     /* rows of one expert handled by one tile; 0 = choose from T*K/E */
+  int32_t use_router;     /* 1: ids / routing_weights are written by the router each forward */
+  int32_t reserved[5];
+} B200MoeShape;
+
+/* Bytes of every workspace buffer the caller must allocate (256-byte aligned
+ * device memory). Field names follow the workspace tensors of PreparedMoE
+ * (moe.py:124-155) and PreparedRankedMoE.ranks (moe_ranked.py:72). */
+typedef struct {
+  size_t output;        /* [T,H] bf16 */
+  size_t counts;        /* [E] int32 */
+  size_t offsets;       /* [E] int32 */
+  size_t cursors;       /* [E] int32, kept for interface parity (zeroed) */
+  size_t tasks;         /* [E+1] int32, exclusive prefix of per-expert token tiles */
+  size_t mapping;       /* [R] int32 */
+  size_t ranks;         /* [R] int32 */
+  size_t grouped_input; /* [R,H] bf16 */
+  size_t activated;     /* [R,I] bf16 */
+  size_t down_output;   /* [R,H] bf16 */
+  size_t status;        /* [1] int32 */
+  size_t scratch;       /* dispatch partial histograms */
+  int32_t token_tile;   /* resolved tile */
+  int32_t schedule;     /* resolved schedule */
+  int32_t launches;     /* kernels one forward enqueues */
+  int32_t reserved;
+} B200MoeWorkspace;
+
+/* Device pointers. x, weights, ids, routing_weights belong to the caller;
+ * the rest is workspace of the sizes b200moe_plan_workspace() reports. */
+typedef struct {
+  const void* x;               /* [T,H] bf16 */
+  const void* router_weight;   /* [E,H] bf16, NULL unless use_router */
+  const void* gate_up;         /* bf16 [E,2I,H]  or packed int32 [E,2I,H/8] */
+  const void* gate_up_scales;  /* bf16 [E,2I,H/128] for W4G128, else NULL */
+  const void* down;            /* bf16 [E,H,I]   or packed int32 [E,H,I/8] */
+  const void* down_scales;     /* bf16 [E,H,I/128] for W4G128, else NULL */
+  void* ids;                   /* [T,K] int32/int64 (input, or router output) */
+  void* routing_weights;       /* [T,K] float32 (input, or router output) */
+  void* output;
+  void* counts;
+  void* offsets;
+  void* cursors;
+  void* tasks;
+  void* mapping;
+  void* ranks;
+  void* grouped_input;
+  void* activated;
+  void* down_output;
+  void* status;
+  void* scratch;
+} B200MoeBuffers;
+
+/* ABI version of the loaded library. */
+int b200moe_abi_version(void);
+
+/* Message of the last failure on this thread ("" if none). */
+const char* b200moe_last_error(void);
+
+/* Validates the shape exactly as prepare_moe does (moe.py:221-235: ranks,
+ * 1<=E<=256, 1<=K<=32, H,I>0, R*max(H,2I) < 2^31) and resolves schedule and
+ * tile. Does not touch the device. */
+int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** plan);
+
+/* Workspace sizes; the allocation itself stays with the caller, as the
+ * reference allocates in prepare_moe (moe.py:237-242). */
+int b200moe_plan_workspace(const B200MoePlan* plan, B200MoeWorkspace* sizes);
+
+/* Binds device addresses on the current device, checks alignment / aliasing
+ * (the TORCH_CHECKs of GateUpPlan, cuda_gate_up.cu:133-165) and encodes the
+ * TMA descriptors. May be called again to rebind. */
+int b200moe_plan_bind(B200MoePlan* plan, const B200MoeBuffers* buffers);
+
+/* One whole forward: PreparedRankedMoE.run() (moe_ranked.py:81-92). No-op for T == 0. */
+int b200moe_forward(B200MoePlan* plan, void* cuda_stream);
+
+/* The five subsystems one at a time, for stage tests and profiling; calling
+ * them in this order equals b200moe_forward(). They replace, in order:
+ * (new: formula of scripts/capture_qwen3_moe_layer0.py:583-587),
+ * _reset+_rank_histogram+_prefix+_rank_dispatch (moe.py:13-43, moe_ranked.py:18-65),
+ * _dynamic_grouped_gate_up_swiglu / GateUpPlan.run / W4GateUpPlan.run
+ *   (moe_fused.py:18-73, cuda_gate_up.cu:167-190, cuda_w4_gate_up.cu:133-151),
+ * _dynamic_grouped as down (moe.py:69-95, 209-210),
+ * _combine (moe.py:109-121). */
+int b200moe_router(B200MoePlan* plan, void* cuda_stream);
+int b200moe_dispatch(B200MoePlan* plan, void* cuda_stream);
+int b200moe_gate_up(B200MoePlan* plan, void* cuda_stream);
+int b200moe_down(B200MoePlan* plan, void* cuda_stream);
+int b200moe_combine(B200MoePlan* plan, void* cuda_stream);
+
+void b200moe_plan_destroy(B200MoePlan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

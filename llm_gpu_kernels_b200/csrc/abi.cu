@@ -1,0 +1,334 @@
+// C ABI of the MoE-layer forward: plan life cycle, argument validation, TMA
+// descriptor encoding, and the launch sequence. See include/b200moe.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include "plan.h"
+
+namespace b200moe {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+namespace {
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+bool tc_shape_ok(const B200MoeShape& s) {
+  return s.hidden % 8 == 0 && s.intermediate % 8 == 0 && s.hidden >= 64 && s.intermediate >= 64 &&
+         s.gate_up_format == B200MOE_WEIGHTS_BF16 && s.down_format == B200MOE_WEIGHTS_BF16;
+}
+
+int auto_token_tile(long long routes, int experts) {
+  // twice the mean rows per expert, as a power of two in [16,128]
+  const long long twice_mu = (2 * routes + experts - 1) / experts;
+  int tile = 16;
+  while (tile < 128 && tile < twice_mu) tile <<= 1;
+  return tile;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D BF16 row-major [rows, cols] tensor, box = 64 columns x box_rows, 128-byte swizzle.
+int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool weights) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return B200MOE_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu box_rows=%u)", static_cast<int>(r),
+              static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols), box_rows);
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return B200MOE_OK;
+  set_error("%s: %s", what, cudaGetErrorString(e));
+  return B200MOE_ERR_CUDA;
+}
+
+int require_bound(const B200MoePlan* p) {
+  if (!p) {
+    set_error("null plan");
+    return B200MOE_ERR_INVALID;
+  }
+  if (!p->bound) {
+    set_error("plan has no buffers bound; call b200moe_plan_bind first");
+    return B200MOE_ERR_STATE;
+  }
+  return B200MOE_OK;
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+
+const char* b200moe_last_error(void) { return g_error; }
+
+int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
+  if (!shape || !out) {
+    set_error("null argument");
+    return B200MOE_ERR_INVALID;
+  }
+  const B200MoeShape& s = *shape;
+  if (s.tokens < 0 || s.experts < 1 || s.experts > 256 || s.hidden <= 0 || s.intermediate <= 0) {
+    set_error("invalid MoE shape; requires T >= 0, E in [1,256], H/I positive");
+    return B200MOE_ERR_INVALID;
+  }
+  if (s.topk < 1 || s.topk > 32) {
+    set_error("expected IDs[T,topk<=32]: topk=%d", s.topk);
+    return B200MOE_ERR_INVALID;
+  }
+  const long long r = static_cast<long long>(s.tokens) * s.topk;
+  const long long widest = s.hidden > 2 * s.intermediate ? s.hidden : 2LL * s.intermediate;
+  if (r >= (1LL << 31) || r * widest >= (1LL << 31)) {
+    set_error("routed/intermediate elements must stay below 2**31 (R=%lld)", r);
+    return B200MOE_ERR_INVALID;
+  }
+  if (s.use_router && s.topk > s.experts) {
+    set_error("router needs topk <= experts");
+    return B200MOE_ERR_INVALID;
+  }
+  if (s.use_router && router_smem_bytes(s.hidden, s.experts) > 227 * 1024) {
+    set_error("router: hidden=%d does not fit the shared-memory staging", s.hidden);
+    return B200MOE_ERR_UNSUPPORTED;
+  }
+  for (int f : {s.gate_up_format, s.down_format}) {
+    if (f != B200MOE_WEIGHTS_BF16) {
+      set_error("weight format %d is not available in this build", f);
+      return B200MOE_ERR_UNSUPPORTED;
+    }
+  }
+  int schedule = s.schedule;
+  if (schedule == B200MOE_SCHEDULE_AUTO) schedule = tc_shape_ok(s) ? B200MOE_SCHEDULE_TCGEN05 : B200MOE_SCHEDULE_GENERIC;
+  if (schedule != B200MOE_SCHEDULE_GENERIC && schedule != B200MOE_SCHEDULE_TCGEN05) {
+    set_error("unknown schedule %d", s.schedule);
+    return B200MOE_ERR_INVALID;
+  }
+  if (schedule == B200MOE_SCHEDULE_TCGEN05 && !tc_shape_ok(s)) {
+    set_error("tcgen05 schedule needs BF16 weights, H and I multiples of 8 and >= 64 (H=%d I=%d)", s.hidden,
+              s.intermediate);
+    return B200MOE_ERR_UNSUPPORTED;
+  }
+  int tile = s.token_tile;
+  if (schedule == B200MOE_SCHEDULE_GENERIC) {
+    if (tile != 0 && tile != kGenericTile) {
+      set_error("the generic schedule uses token_tile %d", kGenericTile);
+      return B200MOE_ERR_INVALID;
+    }
+    tile = kGenericTile;
+  } else if (tile == 0) {
+    tile = auto_token_tile(r, s.experts);
+  } else if (tile != 16 && tile != 32 && tile != 64 && tile != 128 && tile != 256) {
+    set_error("token_tile must be one of 16, 32, 64, 128, 256");
+    return B200MOE_ERR_INVALID;
+  }
+  B200MoePlan* p = new (std::nothrow) B200MoePlan();
+  if (!p) {
+    set_error("out of host memory");
+    return B200MOE_ERR_INVALID;
+  }
+  p->shape = s;
+  p->routes = static_cast<int>(r);
+  p->schedule = schedule;
+  p->token_tile = tile;
+  const int per_warp = round_up(static_cast<int>((r + 511) / 512), 32);
+  p->warp_routes = per_warp < 128 ? 128 : per_warp;
+  p->partitions = static_cast<int>((r + p->warp_routes - 1) / p->warp_routes);
+  const int blocks = (p->partitions + kDispatchWarps - 1) / kDispatchWarps;
+
+  B200MoeWorkspace& w = p->ws;
+  const size_t T = s.tokens, H = s.hidden, I = s.intermediate, E = s.experts, R = r;
+  w.output = T * H * 2;
+  w.counts = E * 4;
+  w.offsets = E * 4;
+  w.cursors = E * 4;
+  w.tasks = (E + 1) * 4;
+  w.mapping = R * 4;
+  w.ranks = R * 4;
+  w.grouped_input = R * H * 2;
+  w.activated = R * I * 2;
+  w.down_output = R * H * 2;
+  w.status = 4;
+  w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks) * 4);
+  w.token_tile = tile;
+  w.schedule = schedule;
+  w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + 6;
+  *out = p;
+  return B200MOE_OK;
+}
+
+int b200moe_plan_workspace(const B200MoePlan* plan, B200MoeWorkspace* sizes) {
+  if (!plan || !sizes) {
+    set_error("null argument");
+    return B200MOE_ERR_INVALID;
+  }
+  *sizes = plan->ws;
+  return B200MOE_OK;
+}
+
+int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
+  if (!p || !b) {
+    set_error("null argument");
+    return B200MOE_ERR_INVALID;
+  }
+  p->bound = false;
+  const B200MoeShape& s = p->shape;
+  int rc = check_cuda(cudaGetDevice(&p->device), "cudaGetDevice");
+  if (rc) return rc;
+  int major = 0;
+  rc = check_cuda(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, p->device), "device attribute");
+  if (rc) return rc;
+  rc = check_cuda(cudaDeviceGetAttribute(&p->num_sms, cudaDevAttrMultiProcessorCount, p->device), "device attribute");
+  if (rc) return rc;
+  if (major != 10) {
+    set_error("this library is built for sm_100a only; device %d has compute capability major %d", p->device, major);
+    return B200MOE_ERR_UNSUPPORTED;
+  }
+  if (s.tokens > 0) {
+    struct Named { const void* ptr; const char* name; };
+    const Named needed[] = {{b->x, "x"}, {b->gate_up, "gate_up"}, {b->down, "down"}, {b->ids, "ids"},
+                            {b->routing_weights, "routing_weights"}, {b->output, "output"}, {b->counts, "counts"},
+                            {b->offsets, "offsets"}, {b->cursors, "cursors"}, {b->tasks, "tasks"},
+                            {b->mapping, "mapping"}, {b->ranks, "ranks"}, {b->grouped_input, "grouped_input"},
+                            {b->activated, "activated"}, {b->down_output, "down_output"}, {b->status, "status"},
+                            {b->scratch, "scratch"}};
+    for (const Named& n : needed) {
+      if (!n.ptr) {
+        set_error("buffer '%s' is null", n.name);
+        return B200MOE_ERR_INVALID;
+      }
+      if (reinterpret_cast<uintptr_t>(n.ptr) % 4) {
+        set_error("buffer '%s' is not 4-byte aligned", n.name);
+        return B200MOE_ERR_INVALID;
+      }
+    }
+    if (s.use_router && !b->router_weight) {
+      set_error("use_router is set but router_weight is null");
+      return B200MOE_ERR_INVALID;
+    }
+    // the output and the workspace must not alias the inputs (cuda_gate_up.cu:150-158)
+    const void* inputs[] = {b->x, b->gate_up, b->down, b->ids, b->routing_weights, b->router_weight};
+    const void* written[] = {b->output, b->grouped_input, b->activated, b->down_output, b->mapping, b->ranks};
+    for (const void* in : inputs)
+      for (const void* wr : written)
+        if (in && in == wr) {
+          set_error("output/workspace buffer aliases an input");
+          return B200MOE_ERR_INVALID;
+        }
+  }
+  p->buf = *b;
+  if (s.tokens > 0 && s.use_router) {
+    const size_t smem = router_smem_bytes(s.hidden, s.experts);
+    if (smem > 48 * 1024) {
+      rc = check_cuda(router_opt_in_smem(smem), "router shared-memory opt-in");
+      if (rc) return rc;
+    }
+  }
+  if (s.tokens > 0 && p->schedule == B200MOE_SCHEDULE_TCGEN05) {
+    const void* aligned16[] = {b->gate_up, b->down, b->grouped_input, b->activated};
+    for (const void* ptr : aligned16)
+      if (reinterpret_cast<uintptr_t>(ptr) % 16) {
+        set_error("tcgen05 schedule: weights and workspace rows must be 16-byte aligned");
+        return B200MOE_ERR_INVALID;
+      }
+    const uint64_t E = s.experts, H = s.hidden, I = s.intermediate, R = p->routes;
+    if ((rc = encode_2d(&p->tm_gate_up_w, b->gate_up, E * 2 * I, H, 128, true))) return rc;
+    if ((rc = encode_2d(&p->tm_grouped, b->grouped_input, R, H, p->token_tile, false))) return rc;
+    if ((rc = encode_2d(&p->tm_down_w, b->down, E * H, I, 128, true))) return rc;
+    if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->token_tile, false))) return rc;
+    if ((rc = configure_tc(*p))) return rc;
+  }
+  p->bound = true;
+  return B200MOE_OK;
+}
+
+int b200moe_router(B200MoePlan* p, void* stream) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (p->shape.tokens == 0 || !p->shape.use_router) return B200MOE_OK;
+  return check_cuda(launch_router(*p, static_cast<cudaStream_t>(stream)), "router launch");
+}
+
+int b200moe_dispatch(B200MoePlan* p, void* stream) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (p->shape.tokens == 0) return B200MOE_OK;
+  return check_cuda(launch_dispatch(*p, static_cast<cudaStream_t>(stream)), "dispatch launch");
+}
+
+int b200moe_gate_up(B200MoePlan* p, void* stream) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (p->shape.tokens == 0) return B200MOE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return check_cuda(p->schedule == B200MOE_SCHEDULE_TCGEN05 ? launch_gate_up_tc(*p, s) : launch_gate_up_generic(*p, s),
+                    "gate_up launch");
+}
+
+int b200moe_down(B200MoePlan* p, void* stream) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (p->shape.tokens == 0) return B200MOE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return check_cuda(p->schedule == B200MOE_SCHEDULE_TCGEN05 ? launch_down_tc(*p, s) : launch_down_generic(*p, s),
+                    "down launch");
+}
+
+int b200moe_combine(B200MoePlan* p, void* stream) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (p->shape.tokens == 0) return B200MOE_OK;
+  return check_cuda(launch_combine(*p, static_cast<cudaStream_t>(stream)), "combine launch");
+}
+
+int b200moe_forward(B200MoePlan* p, void* stream) {
+  int rc;
+  if ((rc = b200moe_router(p, stream))) return rc;
+  if ((rc = b200moe_dispatch(p, stream))) return rc;
+  if ((rc = b200moe_gate_up(p, stream))) return rc;
+  if ((rc = b200moe_down(p, stream))) return rc;
+  return b200moe_combine(p, stream);
+}
+
+void b200moe_plan_destroy(B200MoePlan* p) { delete p; }
+
+}  // extern "C"

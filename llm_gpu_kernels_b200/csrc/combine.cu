@@ -1,0 +1,87 @@
+// Weighted combine back to token order:
+//   out[t,:] = bf16( sum_{slot=0..K-1} float(down_output[mapping[t*K+slot],:]) * rw[t,slot] )
+// in fixed slot order, FP32, multiply and add kept as separate roundings -
+// the semantics of the reference's _combine (moe.py:109-121, launched with
+// enable_fp_fusion=False at moe.py:217). A gather-reduce, not a scatter with
+// atomics, so the result does not depend on scheduling. Routes with
+// mapping < 0 (invalid expert id) contribute nothing (moe.py:117).
+#include <cuda_bf16.h>
+#include "plan.h"
+
+namespace b200moe {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <bool kVec>
+__global__ void __launch_bounds__(kThreads)
+combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict__ mapping,
+               const float* __restrict__ rw, __nv_bfloat16* __restrict__ out, int H, int K) {
+  const int token = blockIdx.x;
+  __shared__ int s_pos[32];
+  __shared__ float s_w[32];
+  if (threadIdx.x < K) {
+    s_pos[threadIdx.x] = mapping[static_cast<size_t>(token) * K + threadIdx.x];
+    s_w[threadIdx.x] = rw[static_cast<size_t>(token) * K + threadIdx.x];
+  }
+  __syncthreads();
+  if (kVec) {
+    const int h = (blockIdx.y * kThreads + threadIdx.x) * 8;
+    if (h >= H) return;
+    float acc[8] = {};
+    for (int slot = 0; slot < K; ++slot) {
+      const int pos = s_pos[slot];
+      if (pos < 0) continue;
+      const float w = s_w[slot];
+      const uint4 p = *reinterpret_cast<const uint4*>(down_out + static_cast<size_t>(pos) * H + h);
+      const uint32_t u[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xffff0000u), w));
+      }
+    }
+    uint4 o;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      ou[j] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(token) * H + h) = o;
+  } else {
+    const int h = blockIdx.y * kThreads + threadIdx.x;
+    if (h >= H) return;
+    float acc = 0.0f;
+    for (int slot = 0; slot < K; ++slot) {
+      const int pos = s_pos[slot];
+      if (pos < 0) continue;
+      acc = __fadd_rn(acc, __fmul_rn(__bfloat162float(down_out[static_cast<size_t>(pos) * H + h]), s_w[slot]));
+    }
+    out[static_cast<size_t>(token) * H + h] = __float2bfloat16_rn(acc);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  auto* d = static_cast<const __nv_bfloat16*>(p.buf.down_output);
+  auto* o = static_cast<__nv_bfloat16*>(p.buf.output);
+  const bool vec = sh.hidden % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(o)) & 15) == 0;
+  if (vec) {
+    dim3 grid(sh.tokens, (sh.hidden / 8 + kThreads - 1) / kThreads);
+    combine_kernel<true><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
+                                                   static_cast<const float*>(p.buf.routing_weights), o, sh.hidden,
+                                                   sh.topk);
+  } else {
+    dim3 grid(sh.tokens, (sh.hidden + kThreads - 1) / kThreads);
+    combine_kernel<false><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
+                                                    static_cast<const float*>(p.buf.routing_weights), o, sh.hidden,
+                                                    sh.topk);
+  }
+  return cudaPeekAtLastError();
+}
+
+}  // namespace b200moe

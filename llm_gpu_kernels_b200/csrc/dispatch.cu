@@ -1,0 +1,185 @@
+// Ranked dispatch: per-expert count, prefix sum, deterministic route -> row
+// permutation, and the row copy into expert-contiguous order.
+//
+// Replaces _reset + _rank_histogram + _prefix + _rank_dispatch of the
+// reference (moe.py:13-43, moe_ranked.py:18-65). The reference takes the rank
+// of a route inside its expert from the return value of a global atomic, so
+// its permutation depends on arrival order; here the rank is the number of
+// earlier routes (by flat index q = token*K + slot) that chose the same
+// expert, which is the stable order of argsort(ids, stable=True). No global
+// atomics are used, so counts / offsets / ranks / mapping are bit-reproducible.
+//
+// Three kernels:
+//  count   - every warp owns `warp_routes` consecutive routes and walks them 32
+//            at a time in order: __match_any_sync gives the lanes with the same
+//            expert, so rank-in-partition = running warp histogram + number of
+//            lower lanes with that expert. Writes the rank inside the
+//            partition to ranks[q] and the partition histogram to scratch.
+//  scan    - one block: per expert an exclusive scan over the partitions
+//            (scratch becomes the partition's base rank), counts, offsets,
+//            the token-tile prefix `tasks`, cursors = 0, and the status word.
+//  permute - ranks[q] += base; mapping[q] = offsets[id] + ranks[q]; one warp
+//            copies the token's row to grouped_input[mapping[q]].
+#include <cuda_bf16.h>
+#include "plan.h"
+
+namespace b200moe {
+namespace {
+
+constexpr int kWarps = kDispatchWarps;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxExperts = 256;
+
+// scratch layout: int32 hist[partitions][E], then int32 flags[blocks]
+template <typename IdT>
+__global__ void __launch_bounds__(kThreads)
+dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
+                      int* __restrict__ hist, int* __restrict__ flags, int R, int E, int warp_routes,
+                      int partitions) {
+  __shared__ int warp_hist[kWarps][kMaxExperts];
+  __shared__ int block_flags;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = blockIdx.x * kWarps + warp;
+  if (threadIdx.x == 0) block_flags = 0;
+  for (int e = lane; e < E; e += 32) warp_hist[warp][e] = 0;
+  __syncthreads();
+  int my_flags = 0;
+  if (part < partitions) {
+    const int begin = part * warp_routes;
+    const int end = min(R, begin + warp_routes);
+    for (int base = begin; base < end; base += 32) {
+      const int q = base + lane;
+      const bool in = q < end;
+      long long id = in ? static_cast<long long>(ids[q]) : -1;
+      const float w = in ? rw[q] : 0.0f;
+      const bool valid = in && id >= 0 && id < E;
+      if (in && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
+      if (in && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;  // false for NaN too
+      const int key = valid ? static_cast<int>(id) : E;  // E = "no expert"
+      const unsigned peers = __match_any_sync(0xffffffffu, key);
+      const int below = __popc(peers & ((1u << lane) - 1u));
+      int rank = -1;
+      if (valid) {
+        rank = warp_hist[warp][key] + below;
+      }
+      __syncwarp();
+      if (valid && below == 0) warp_hist[warp][key] += __popc(peers);
+      __syncwarp();
+      if (in) ranks[q] = rank;
+    }
+    for (int e = lane; e < E; e += 32) hist[static_cast<size_t>(part) * E + e] = warp_hist[warp][e];
+  }
+  if (my_flags) atomicOr(&block_flags, my_flags);
+  __syncthreads();
+  if (threadIdx.x == 0) flags[blockIdx.x] = block_flags;
+}
+
+__global__ void __launch_bounds__(kMaxExperts)
+dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int* __restrict__ counts,
+                     int* __restrict__ offsets, int* __restrict__ cursors, int* __restrict__ tasks,
+                     int* __restrict__ status, int E, int partitions, int blocks, int token_tile) {
+  __shared__ int s_count[kMaxExperts];
+  __shared__ int s_tiles[kMaxExperts];
+  __shared__ int s_flags;
+  const int e = threadIdx.x;
+  if (e == 0) s_flags = 0;
+  __syncthreads();
+  int total = 0;
+  if (e < E) {
+    for (int p = 0; p < partitions; ++p) {
+      const size_t i = static_cast<size_t>(p) * E + e;
+      const int c = hist[i];
+      hist[i] = total;
+      total += c;
+    }
+  }
+  int f = 0;
+  for (int b = e; b < blocks; b += blockDim.x) f |= flags[b];
+  if (f) atomicOr(&s_flags, f);
+  s_count[e] = e < E ? total : 0;
+  s_tiles[e] = e < E ? (total + token_tile - 1) / token_tile : 0;
+  __syncthreads();
+  // E <= 256: a serial exclusive prefix per thread over shared memory is cheap and exact
+  if (e < E) {
+    int off = 0, toff = 0;
+    for (int j = 0; j < e; ++j) { off += s_count[j]; toff += s_tiles[j]; }
+    counts[e] = total;
+    offsets[e] = off;
+    cursors[e] = 0;
+    tasks[e] = toff;
+    if (e == E - 1) tasks[E] = toff + s_tiles[e];
+  }
+  if (e == 0) *status = s_flags;
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kThreads)
+dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restrict__ ids,
+                        const int* __restrict__ hist, const int* __restrict__ offsets,
+                        int* __restrict__ ranks, int* __restrict__ mapping,
+                        __nv_bfloat16* __restrict__ grouped, int R, int E, int H, int K, int warp_routes) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = blockIdx.x * kWarps + warp;
+  if (q >= R) return;
+  const long long id = static_cast<long long>(ids[q]);
+  const bool valid = id >= 0 && id < E;
+  int pos = -1;
+  if (lane == 0) {  // one lane owns the read-modify-write of ranks[q]
+    if (valid) {
+      const int part = q / warp_routes;
+      const int rank = ranks[q] + hist[static_cast<size_t>(part) * E + static_cast<int>(id)];
+      pos = offsets[id] + rank;
+      ranks[q] = rank;
+    }
+    mapping[q] = pos;
+  }
+  pos = __shfl_sync(0xffffffffu, pos, 0);
+  if (!valid) return;
+  const __nv_bfloat16* src = x + static_cast<size_t>(q / K) * H;
+  __nv_bfloat16* dst = grouped + static_cast<size_t>(pos) * H;
+  if ((H & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grouped)) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = lane; i < H / 8; i += 32) d4[i] = s4[i];
+  } else {
+    for (int i = lane; i < H; i += 32) dst[i] = src[i];
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  const int R = p.routes, E = sh.experts;
+  const int blocks = (p.partitions + kWarps - 1) / kWarps;
+  int* hist = static_cast<int*>(p.buf.scratch);
+  int* flags = hist + static_cast<size_t>(p.partitions) * E;
+  int* ranks = static_cast<int*>(p.buf.ranks);
+  auto* rw = static_cast<const float*>(p.buf.routing_weights);
+  if (sh.ids_are_int64) {
+    dispatch_count_kernel<long long><<<blocks, kThreads, 0, s>>>(
+        static_cast<const long long*>(p.buf.ids), rw, ranks, hist, flags, R, E, p.warp_routes, p.partitions);
+  } else {
+    dispatch_count_kernel<int><<<blocks, kThreads, 0, s>>>(
+        static_cast<const int*>(p.buf.ids), rw, ranks, hist, flags, R, E, p.warp_routes, p.partitions);
+  }
+  dispatch_scan_kernel<<<1, kMaxExperts, 0, s>>>(
+      hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
+      static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status), E,
+      p.partitions, blocks, p.token_tile);
+  const int pblocks = (R + kWarps - 1) / kWarps;
+  auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
+  auto* grouped = static_cast<__nv_bfloat16*>(p.buf.grouped_input);
+  if (sh.ids_are_int64) {
+    dispatch_permute_kernel<long long><<<pblocks, kThreads, 0, s>>>(
+        x, static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
+        static_cast<int*>(p.buf.mapping), grouped, R, E, sh.hidden, sh.topk, p.warp_routes);
+  } else {
+    dispatch_permute_kernel<int><<<pblocks, kThreads, 0, s>>>(
+        x, static_cast<const int*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
+        static_cast<int*>(p.buf.mapping), grouped, R, E, sh.hidden, sh.topk, p.warp_routes);
+  }
+  return cudaPeekAtLastError();
+}
+
+}  // namespace b200moe

@@ -1,0 +1,397 @@
+// Ragged grouped GEMM on the Blackwell tensor cores: TMA-fed tcgen05.mma with
+// the accumulators in tensor memory, one persistent warp-specialised CTA per SM.
+//
+// Replaces the reference's gate/up + SwiGLU kernels (moe_fused.py:18-73,
+// cuda_gate_up.cu:53-131) and its down projection (_dynamic_grouped,
+// moe.py:69-95). Written for sm_100a from scratch:
+//
+//  * The weights are the M operand ("swap-AB"): one tile is 128 output
+//    channels x `token_tile` rows of one expert. D[channel][row] lives in
+//    tensor memory with the channel on the TMEM lane, so the MMA N dimension
+//    is the (small, ragged) number of rows of the expert and is set per tile in
+//    the instruction descriptor: an expert with 5 rows costs an N=16 MMA and
+//    its weights are streamed from HBM exactly once.
+//  * gate and up tiles share the activation tile and accumulate into two TMEM
+//    column ranges of the same lanes, so SwiGLU needs no data exchange: the
+//    thread that owns channel c reads gate[c][n] and up[c][n], and nothing is
+//    rounded before silu(g)*u (one BF16 rounding, at the store).
+//  * Expert segments are dense and ragged (no padding): an activation box may
+//    run into the next expert's rows or past the end (zero fill); those
+//    columns of D are simply not stored. A weight box may run past the
+//    expert's channels; those lanes are not stored.
+//  * Tiles are enumerated on the device from the `tasks` prefix the dispatch
+//    wrote (tile -> expert by binary search), round-robin over the persistent
+//    CTAs, so the grid is shape-only and the launch is graph-capturable.
+//  * warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-5 =
+//    epilogue (one TMEM lane quarter each). Shared-memory stages and the TMEM
+//    accumulators are double buffered through mbarriers; every wait is bounded
+//    and on expiry raises B200MOE_STATUS_TIMEOUT and leaves cleanly.
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include "plan.h"
+
+namespace b200moe {
+namespace {
+
+constexpr int kBlockK = 64;                    // bf16 per k-block: 128 bytes = one swizzle row
+constexpr int kTileM = 128;                    // output channels per tile (UMMA M)
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 12;
+constexpr int kMaxExperts = 256;
+constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
+constexpr int kCtrlBytes = 4096;
+constexpr int kSmemLimit = 232448;             // 227 KB opt-in limit per CTA
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // 1 s per wait
+
+struct Ctrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+  int tasks[kMaxExperts + 1];
+  int offsets[kMaxExperts];
+  int counts[kMaxExperts];
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the wait was given up (by this thread on
+// expiry, or because another role of the CTA already gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* c, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile int*>(&c->abort)) return false;
+      if (global_timer() - start > kWaitLimitNs) {
+        *reinterpret_cast<volatile int*>(&c->abort) = 1;
+        atomicOr(status, B200MOE_STATUS_TIMEOUT);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile written by TMA with 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart (SBO), version 1 (sm_100), layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// kind::f16, BF16 x BF16 -> FP32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct Tile {
+  int expert, ct, row0, rows, n_eff;
+};
+
+// item -> (expert, channel tile, token tile). Items of one expert are ordered
+// channel tile major, token tile fastest, so CTAs running side by side share a
+// weight tile (L2) when an expert has several token tiles.
+__device__ __forceinline__ Tile decode_tile(const Ctrl* c, int item, int E, int n_ct, int token_tile) {
+  int lo = 0, hi = E;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (item >= c->tasks[mid + 1] * n_ct) lo = mid + 1; else hi = mid;
+  }
+  Tile t;
+  t.expert = lo;
+  const int local = item - c->tasks[lo] * n_ct;
+  const int tiles = c->tasks[lo + 1] - c->tasks[lo];
+  t.ct = local / tiles;
+  const int tt = local - t.ct * tiles;
+  t.row0 = c->offsets[lo] + tt * token_tile;
+  t.rows = min(token_tile, c->counts[lo] - tt * token_tile);
+  t.n_eff = max(16, (t.rows + 15) & ~15);
+  return t;
+}
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_act,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ g_offsets,
+                       const int* __restrict__ g_counts, const int* __restrict__ g_tasks, int* __restrict__ status,
+                       int E, int n_out, int k_dim, int w_rows_per_expert, int token_tile, int num_stages,
+                       int stream_weights) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t stage_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
+  unsigned char* stages = smem_raw + stage_off;
+  constexpr uint32_t kWBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;
+  const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
+  const uint32_t stage_bytes = kWBytes + act_bytes;
+  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i <= E; i += kThreads) c->tasks[i] = g_tasks[i];
+  for (int i = threadIdx.x; i < E; i += kThreads) {
+    c->offsets[i] = g_offsets[i];
+    c->counts[i] = g_counts[i];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < num_stages; ++s) {
+      mbar_init(&c->full[s], 1);
+      mbar_init(&c->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_empty[a], 128);
+    }
+    mbar_init(&c->drain, 1);
+    c->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&c->tmem_base)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
+
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const int num_kb = (k_dim + kBlockK - 1) / kBlockK;
+  const int total_items = c->tasks[E] * n_ct;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      uint64_t pol_w, pol_act;
+      if (stream_weights) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_w));
+      else asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_w));
+      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_act));
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+        const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->empty[stage], phase ^ 1u, c, status)) { ok = false; break; }
+          unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
+          mbar_expect_tx(&c->full[stage], stage_bytes);
+          tma_load_2d(st, &tm_w, &c->full[stage], kb * kBlockK, w_row, pol_w);
+          if (kGateUp) tma_load_2d(st + kWTileBytes, &tm_w, &c->full[stage], kb * kBlockK, w_row + n_out, pol_w);
+          tma_load_2d(st + kWBytes, &tm_act, &c->full[stage], kb * kBlockK, t.row0, pol_act);
+          ++issued;
+          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // Never leave with copies in flight: wait (bounded) for the last copy of
+      // every stage. On the normal path these have long completed.
+      const long long first = issued > num_stages ? issued - num_stages : 0;
+      for (long long i = first; i < issued; ++i) {
+        const int s = static_cast<int>(i % num_stages);
+        const uint32_t ph = static_cast<uint32_t>((i / num_stages) & 1);
+        const unsigned long long start = global_timer();
+        while (!mbar_try_wait(&c->full[s], ph)) {
+          if (global_timer() - start > kWaitLimitNs) { atomicOr(status, B200MOE_STATUS_TIMEOUT); break; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+        const uint32_t idesc = umma_idesc(t.n_eff);
+        if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, c, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
+        const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->full[stage], phase, c, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
+          const uint32_t a_addr = w_addr + kWBytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
+            const uint64_t bdesc = umma_desc(a_addr + k * kUmmaK * 2);
+            umma(d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+            if (kGateUp) umma(d_up, umma_desc(w_addr + kWTileBytes + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+          }
+          umma_commit(&c->empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&c->tmem_full[acc]);
+        if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) {  // gave up: let the MMAs already issued finish before TMEM is freed
+        umma_commit(&c->drain);
+        const unsigned long long start = global_timer();
+        while (!mbar_try_wait(&c->drain, 0)) {
+          if (global_timer() - start > kWaitLimitNs) break;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+      // warp-uniform outcome: the TMEM loads below need the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, c, status))) break;
+      tc_fence_after();
+      const int channel = t.ct * kTileM + quarter * 32 + lane;
+      const bool ch_ok = channel < n_out;
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
+      __nv_bfloat16* dst = out + static_cast<size_t>(t.row0) * n_out + channel;
+      for (int n0 = 0; n0 < t.n_eff; n0 += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + n0, g);
+        if (kGateUp) tmem_ld16(taddr + token_tile + n0, u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int n = n0 + j;
+          float v = __uint_as_float(g[j]);
+          if (kGateUp) v = (v / (1.0f + __expf(-v))) * __uint_as_float(u[j]);
+          if (ch_ok && n < t.rows) dst[static_cast<size_t>(n) * n_out] = __float2bfloat16_rn(v);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&c->tmem_empty[acc]);
+      if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+int stages_for(bool gate_up, int token_tile, int* smem_bytes) {
+  const int stage = (gate_up ? 2 : 1) * static_cast<int>(kWTileBytes) + token_tile * 128;
+  int stages = (kSmemLimit - kCtrlBytes - 1024) / stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  *smem_bytes = kCtrlBytes + 1024 + stages * stage;
+  return stages;
+}
+
+template <bool kGateUp>
+cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  const int n_out = kGateUp ? sh.intermediate : sh.hidden;
+  const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
+  const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
+  const int smem = kGateUp ? p.gemm_smem_gate_up : p.gemm_smem_down;
+  const int stages = kGateUp ? p.gemm_stages_gate_up : p.gemm_stages_down;
+  // weights are streamed (evict-first) when an expert rarely has a second token tile
+  const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
+  grouped_gemm_tc_kernel<kGateUp><<<grid, kThreads, smem, s>>>(
+      kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
+      static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
+      static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
+      static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
+      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, stages, stream_weights);
+  return cudaPeekAtLastError();
+}
+
+}  // namespace
+
+int configure_tc(B200MoePlan& p) {
+  p.gemm_stages_gate_up = stages_for(true, p.token_tile, &p.gemm_smem_gate_up);
+  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down);
+  if (p.gemm_stages_gate_up < 2 || p.gemm_stages_down < 2) {
+    set_error("token_tile %d leaves fewer than 2 shared-memory stages", p.token_tile);
+    return B200MOE_ERR_INVALID;
+  }
+  // the opt-in is per kernel, not per plan: always raise it to the device limit
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemLimit);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(shared memory) failed: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s) { return launch_tc<true>(p, s); }
+cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s) { return launch_tc<false>(p, s); }
+
+}  // namespace b200moe

@@ -1,0 +1,52 @@
+// Internal plan object behind the C ABI and the launchers of each subsystem.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "../../include/b200moe.h"
+
+struct B200MoePlan {
+  B200MoeShape shape{};
+  B200MoeBuffers buf{};
+  B200MoeWorkspace ws{};
+  bool bound = false;
+  int device = -1;
+  int num_sms = 0;
+  int routes = 0;          // R = T*K
+  int token_tile = 0;      // rows of one expert per tile (tasks granularity)
+  int schedule = 0;
+  // dispatch partition: each warp ranks `warp_routes` consecutive routes
+  int warp_routes = 0;
+  int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
+  // TMA descriptors (tcgen05 schedule)
+  CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128
+  CUtensorMap tm_grouped{};     // [R, H] bf16, box 64 x token_tile
+  CUtensorMap tm_down_w{};      // [E*H, I] bf16, box 64 x 128
+  CUtensorMap tm_activated{};   // [R, I] bf16, box 64 x token_tile
+  int gemm_smem_gate_up = 0, gemm_stages_gate_up = 0;
+  int gemm_smem_down = 0, gemm_stages_down = 0;
+};
+
+namespace b200moe {
+
+void set_error(const char* fmt, ...);
+
+// Each returns a cudaError_t from the launch (cudaPeekAtLastError), never synchronises.
+cudaError_t launch_router(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_generic(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_down_generic(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
+
+size_t router_smem_bytes(int hidden, int experts);
+cudaError_t router_opt_in_smem(size_t bytes);
+
+// One-time per-plan set-up of the tcgen05 kernels (smem opt-in, stage counts).
+int configure_tc(B200MoePlan& p);
+
+constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
+constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels
+
+}  // namespace b200moe
