@@ -1,0 +1,339 @@
+"""Benchmark of the MoE-layer forward (router -> ranked dispatch -> gate/up +
+SwiGLU -> down -> weighted combine) on the Qwen3-30B-A3B layer shape.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this implementation
+    python bench.py --impl reference --steps K --warmup W    # FP32 CPU oracle on the host cores
+
+One "step" is one forward of the layer over one batch of T synthetic tokens
+(seeded N(0,1) activations, N(0,0.02) weights; no checkpoint or trace is
+read). The headline line is T=1024; T=17 and T=193 are reported in ``by_tokens``.
+The device-timed value is a CUDA-graph replay of the forward with all inputs
+resident in HBM; the 1.2 GB of expert weights exceed the 126 MB L2, so every
+step streams them from HBM again. ``e2e`` goes through the public prepared-MoE
+API with host buffers: pinned-host activations are copied in and the BF16
+result is copied back inside the timed region. Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+QWEN = dict(experts=128, hidden=2048, intermediate=768, topk=8)
+TOKENS = (17, 193, 1024)
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def seeded_weights(seed=0, wscale=0.02, **shape):
+    e, h, i = shape["experts"], shape["hidden"], shape["intermediate"]
+    g = torch.Generator().manual_seed(seed)
+    wr = (wscale * torch.randn(e, h, generator=g)).bfloat16()
+    gate_up = torch.empty(e, 2 * i, h, dtype=torch.bfloat16)
+    down = torch.empty(e, h, i, dtype=torch.bfloat16)
+    for k in range(e):  # per-expert draws bound the FP32 temporaries
+        gate_up[k] = (wscale * torch.randn(2 * i, h, generator=g)).bfloat16()
+    for k in range(e):
+        down[k] = (wscale * torch.randn(h, i, generator=g)).bfloat16()
+    return wr, gate_up, down, g
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        n = self._nvml
+        names = {"hw_slowdown": n.nvmlClocksEventReasonHwSlowdown if hasattr(n, "nvmlClocksEventReasonHwSlowdown")
+                 else n.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown",
+                                                getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0)),
+                 "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown",
+                                                getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0)),
+                 "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap",
+                                         getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0))}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
+                try:
+                    mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                except Exception:
+                    mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                self.reasons.update(k for k, bit in names.items() if bit and mask & bit)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nvml:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def event_ms(fn, steps, stream):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    end.record(stream)
+    end.synchronize()
+    return start.elapsed_time(end) / steps
+
+
+def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx):
+    """Prepare one layer at T tokens and time it: graph replay, eager, gate/up stage, end to end."""
+    from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    from oracle.moe_oracle import algorithmic_work
+    wr, gate_up, down, x_host = weights
+    e, h, i, k = QWEN["experts"], QWEN["hidden"], QWEN["intermediate"], QWEN["topk"]
+    x = x_host.to(dev)
+    ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
+    rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
+    prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr)
+    base = prepared.base
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(max(3, warmup)):
+        prepared.run()
+    torch.cuda.synchronize(dev)
+    prepared.check_inputs()
+    active = int((base.counts > 0).sum())
+    max_rows = int(base.counts.max())
+
+    graph = torch.cuda.CUDAGraph()
+    capture = torch.cuda.Stream(device=dev)
+    with torch.cuda.graph(graph, stream=capture):
+        prepared.run()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(dev)
+
+    def barrier():
+        if dist_ctx is not None:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    barrier()
+    graph_ms = event_ms(graph.replay, steps, stream)
+    barrier()
+    eager_ms = event_ms(prepared.run, steps, stream)
+
+    # dominant kernel (gate/up + SwiGLU): events around that stage alone, inside a full forward
+    launches = {l.name: l for l in prepared.launches}
+    stage_ms = {name: 0.0 for name in launches}
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in launches]
+    reps = min(steps, 50)
+    for _ in range(reps):
+        for (a, b), launch in zip(evs, prepared.launches):
+            a.record(stream)
+            launch.run()
+            b.record(stream)
+        torch.cuda.synchronize(dev)
+        for (a, b), launch in zip(evs, prepared.launches):
+            stage_ms[launch.name] += a.elapsed_time(b) / reps
+
+    # end to end through the public API with host buffers
+    x_pinned = x_host.clone().pin_memory()
+    out_pinned = torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_pinned, non_blocking=True)
+        out_pinned.copy_(prepared.run(), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_ms = event_ms(e2e_step, steps, stream)
+    torch.cuda.synchronize(dev)
+
+    flops, nbytes = algorithmic_work(tokens, e, k, h, i, active)
+    t_roof_ms = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)) * 1e3
+    gate_up_bytes = active * 2 * i * h * 2 + tokens * k * h * 2 + tokens * k * i * 2
+    gate_up_gbs = gate_up_bytes / (stage_ms["gate_up_swiglu"] * 1e-3) / 1e9
+    return {
+        "tokens": tokens, "ms_graph": graph_ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms,
+        "tokens_per_s": tokens / (graph_ms * 1e-3), "tokens_per_s_e2e": tokens / (e2e_ms * 1e-3),
+        "active_experts": active, "max_rows_per_expert": max_rows, "token_tile": base.token_tile,
+        "schedule": base.schedule, "alg_flops": flops, "alg_bytes": nbytes,
+        "layer_hbm_gbs": nbytes / (graph_ms * 1e-3) / 1e9, "layer_roofline_frac": t_roof_ms / graph_ms,
+        "stage_ms": stage_ms, "gate_up_alg_bytes": gate_up_bytes, "gate_up_gbs": gate_up_gbs,
+        "h2d_bytes": tokens * h * 2, "d2h_bytes": tokens * h * 2, "launches": 6 + 1,
+    }
+
+
+def cpu_baseline(tokens, weights_cpu, x_cpu, repeats):
+    """Oracle port (router + FP32 expert loop) on the host cores; best of `repeats` after one warm-up."""
+    from oracle import moe_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    wr, gate_up, down = weights_cpu
+    O.moe_layer_oracle(x_cpu, wr, gate_up, down, QWEN["topk"])
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.moe_layer_oracle(x_cpu, wr, gate_up, down, QWEN["topk"])
+        best = min(best, time.perf_counter() - t0)
+    return {"value": tokens / best, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"router_oracle + moe_oracle, one forward of T={tokens} tokens (full workload), "
+                      f"best of {repeats} after 1 warm-up, {best * 1e3:.1f} ms"}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    tokens = args.tokens
+    wr, gate_up, down, g = seeded_weights(**QWEN)
+    x = torch.randn(tokens, QWEN["hidden"], generator=g).bfloat16()
+    from oracle import moe_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    for _ in range(max(1, min(args.warmup, 3))):
+        O.moe_layer_oracle(x, wr, gate_up, down, QWEN["topk"])
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.moe_layer_oracle(x, wr, gate_up, down, QWEN["topk"])
+    ms = (time.perf_counter() - t0) / steps * 1e3
+    value = tokens / (ms * 1e-3)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"Qwen3-30B-A3B MoE layer forward, T={tokens}, E128 H2048 I768 top-8, "
+                                   "FP32 CPU oracle (port of the reference's moe_reference + router formula)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"{steps} forwards of T={tokens} tokens on the host cores"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--tokens", type=int, default=1024, help="headline batch size")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (there is no CPU fallback); use --impl reference for the CPU oracle")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist_ctx = None
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+        dist_ctx = True
+    peaks = measured_peaks()
+
+    wr, gate_up, down, g = seeded_weights(**QWEN)
+    weights_cpu = (wr, gate_up, down)
+    xs = {t: torch.randn(t, QWEN["hidden"], generator=g).bfloat16() for t in TOKENS}
+    if args.tokens not in xs:
+        xs[args.tokens] = torch.randn(args.tokens, QWEN["hidden"], generator=g).bfloat16()
+    wr_d, gate_up_d, down_d = (t.to(dev) for t in weights_cpu)
+
+    results = {}
+    with ClockSampler(local_rank) as clocks:
+        for tokens in sorted(xs):
+            results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
+                                           args.warmup, peaks, dist_ctx)
+    head = results[args.tokens]
+
+    # every rank runs the same full layer on its own batch (replicas); max over ranks
+    ms, e2e_ms = head["ms_graph"], head["ms_e2e"]
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = cpu_baseline(args.tokens, weights_cpu, xs[args.tokens], repeats=3)
+
+    line = {
+        "metric": METRIC, "value": world * args.tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Qwen3-30B-A3B MoE layer forward (router+dispatch+gate/up SwiGLU+down+combine), "
+                               f"T={args.tokens} tokens per GPU, E128 H2048 I768 top-8, BF16",
+                   "timing": "CUDA-graph replay of one forward per step, CUDA events",
+                   "l2": "inputs larger than L2: 1.2 GB of expert weights streamed per step",
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "token_tile": head["token_tile"], "schedule": head["schedule"],
+                   "active_experts": head["active_experts"]},
+        "roofline": {"bound": "hbm", "achieved": head["gate_up_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": head["gate_up_gbs"] / peaks["hbm_gbs"], "traffic": None,
+                     "kernel": "grouped_gemm_tc_kernel<gate_up>", "peak_source": peaks["source"],
+                     "alg_bytes_per_launch": head["gate_up_alg_bytes"],
+                     "ms_per_launch": head["stage_ms"]["gate_up_swiglu"],
+                     "layer": {"alg_bytes": head["alg_bytes"], "alg_flops": head["alg_flops"],
+                               "achieved_gbs": head["layer_hbm_gbs"], "frac": head["layer_roofline_frac"]}},
+        "e2e": {"value": world * args.tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": head["h2d_bytes"], "d2h_bytes_per_step": head["d2h_bytes"],
+                "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps * head["launches"],
+        "clocks": clocks.summary(),
+        "by_tokens": {str(t): {k: v for k, v in r.items() if k not in ("tokens",)} for t, r in results.items()},
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

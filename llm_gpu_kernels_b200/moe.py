@@ -1,0 +1,236 @@
+"""Prepared MoE layer: fixed buffers and shapes, values change in place.
+
+Host-side mirror of the reference's ``PreparedMoE`` / ``prepare_moe``
+(reference moe.py:124-245): same argument order, same validation and error
+types, same attribute names for every buffer, the same life cycle (allocate
+and run once at prepare, then ``run()`` enqueues kernels on the current stream
+with no allocation, no host read and no synchronisation, so it can be captured
+in a CUDA graph). The kernels behind it are the sm_100a library reached
+through the C ABI of ``include/b200moe.h``; nothing here computes on the host.
+
+Two additions to the reference interface, both keyword-only:
+``router_weight`` ([E,H] BF16) puts the top-k softmax router in front of the
+fixed-route path - ``ids`` and ``routing_weights`` then are outputs rewritten by
+every ``run()``; ``schedule`` / ``token_tile`` pin the shape-only kernel choice.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _native
+from .gemm import GemmConfig
+
+STAGE_NAMES = ("router", "dispatch", "gate_up_swiglu", "down", "combine")
+_SCHEDULES = {None: _native.SCHEDULE_AUTO, "auto": _native.SCHEDULE_AUTO,
+              "generic": _native.SCHEDULE_GENERIC, "tcgen05": _native.SCHEDULE_TCGEN05}
+
+
+def _input(tensor, ndim):
+    # reference gemm.py:105-107
+    if (not isinstance(tensor, torch.Tensor) or tensor.ndim != ndim or tensor.dtype != torch.bfloat16
+            or not tensor.is_cuda or not tensor.is_contiguous()):
+        raise ValueError(f"expected contiguous CUDA BF16 tensor with {ndim} dimensions")
+
+
+@dataclass(frozen=True)
+class StageLaunch:
+    """One subsystem of the forward; ``run()`` enqueues it on the current stream."""
+    name: str
+    _call: object = field(repr=False)
+    _plan: object = field(repr=False)
+    _device: torch.device = field(repr=False)
+
+    def run(self):
+        _native.check(self._call(self._plan, torch.cuda.current_stream(self._device).cuda_stream))
+
+
+@dataclass
+class PreparedMoE:
+    """Fixed buffers/shapes; runtime ids and values may change in place.
+
+    Attribute names follow reference moe.py:131-149. ``projected`` (the unfused
+    [R,2I] gate/up result of the reference) is never materialised here - SwiGLU
+    runs on the accumulators - and is kept as an empty tensor for interface
+    parity. ``ranks`` and ``scratch`` are this implementation's dispatch workspace.
+    Status flags invalid runtime values; ``check_inputs`` is an explicit
+    synchronising debug operation, never part of ``run``. The caller orders
+    streams and never runs one workspace concurrently (docs/MOE_USAGE.md:95-108).
+    """
+    x: torch.Tensor
+    gate_up: torch.Tensor
+    down: torch.Tensor
+    ids: torch.Tensor
+    routing_weights: torch.Tensor
+    output: torch.Tensor
+    counts: torch.Tensor
+    offsets: torch.Tensor
+    cursors: torch.Tensor
+    tasks: torch.Tensor
+    mapping: torch.Tensor
+    grouped_input: torch.Tensor
+    projected: torch.Tensor
+    activated: torch.Tensor
+    down_output: torch.Tensor
+    status: torch.Tensor
+    config: GemmConfig
+    kernels: dict = field(default_factory=dict)
+    ranks: torch.Tensor = None
+    scratch: torch.Tensor = None
+    router_weight: torch.Tensor = None
+    schedule: str = ""
+    token_tile: int = 0
+    launches: tuple = ()
+    _plan: object = field(default=None, repr=False)
+    _forward: object = field(default=None, repr=False)
+
+    @property
+    def workspace_bytes(self):
+        # the tensors reference moe.py:151-155 counts, plus this implementation's scratch
+        return sum(t.numel() * t.element_size() for t in
+                   (self.counts, self.offsets, self.cursors, self.tasks, self.mapping, self.grouped_input,
+                    self.projected, self.activated, self.down_output, self.status, self.scratch))
+
+    def check_inputs(self):
+        flags = int(self.status.item())
+        if flags:
+            raise ValueError(f"invalid runtime MoE inputs: GPU status={flags} "
+                             "(1=IDs, 2=nonfinite weights, 4=kernel wait timeout)")
+
+    def _stage(self, index):
+        if self.x.shape[0]:
+            self.launches[index].run()
+
+    def route(self):
+        """Router (only when prepared with ``router_weight``)."""
+        self._stage(0)
+
+    def dispatch(self):
+        self._stage(1)
+
+    def project(self):
+        """Gate/up grouped GEMM with SwiGLU fused (writes ``activated``)."""
+        self._stage(2)
+
+    def activate(self):
+        """No separate launch: SwiGLU is fused into :meth:`project`."""
+
+    def down_project(self):
+        self._stage(3)
+
+    def combine(self):
+        self._stage(4)
+
+    def run(self):
+        if self.x.shape[0] == 0:
+            return self.output
+        device = self.x.device
+        if torch.cuda.current_device() == device.index:
+            _native.check(self._forward(self._plan, torch.cuda.current_stream(device).cuda_stream))
+        else:
+            with torch.cuda.device(device):
+                _native.check(self._forward(self._plan, torch.cuda.current_stream(device).cuda_stream))
+        return self.output
+
+    def __del__(self):
+        plan, self._plan = self._plan, None
+        if plan is not None:
+            try:
+                _native.load().b200moe_plan_destroy(plan)
+            except Exception:  # interpreter shutdown
+                pass
+
+
+def _validate(x, gate_up, down, ids, routing_weights, router_weight):
+    for tensor, rank in ((x, 2), (gate_up, 3), (down, 3)):
+        _input(tensor, rank)
+    e, h, intermediate = down.shape
+    if (not 0 < e <= 256 or h <= 0 or intermediate <= 0 or x.shape[1] != h
+            or tuple(gate_up.shape) != (e, 2 * intermediate, h)):
+        raise ValueError("invalid MoE shape; prototype requires E in [1,256], H/I positive")
+    if (not isinstance(ids, torch.Tensor) or not isinstance(routing_weights, torch.Tensor) or ids.ndim != 2
+            or ids.dtype not in (torch.int32, torch.int64) or ids.shape[0] != x.shape[0]
+            or not 0 < ids.shape[1] <= 32 or routing_weights.shape != ids.shape
+            or routing_weights.dtype != torch.float32):
+        raise ValueError("expected CUDA IDs[T,topk<=32] and FP32 weights of identical shape")
+    if any(t.device != x.device or not t.is_contiguous() for t in (gate_up, down, ids, routing_weights)):
+        raise ValueError("all MoE tensors must be contiguous and on the same CUDA device")
+    r = ids.numel()
+    if r >= 2**31 or r * max(h, 2 * intermediate) >= 2**31:
+        raise ValueError("prototype vector indexing requires routed/intermediate elements < 2**31")
+    if router_weight is not None:
+        _input(router_weight, 2)
+        if tuple(router_weight.shape) != (e, h) or router_weight.device != x.device:
+            raise ValueError("router_weight must be [E,H] BF16 on the same device")
+        if ids.shape[1] > e:
+            raise ValueError("router needs topk <= experts")
+
+
+def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
+             token_tile=0, config=None, warm=True):
+    """Validate, allocate the workspace, bind the native plan, run one forward."""
+    _validate(x, gate_up, down, ids, routing_weights, router_weight)
+    if schedule not in _SCHEDULES:
+        raise ValueError(f"unknown schedule {schedule!r}; expected one of auto/generic/tcgen05")
+    lib = _native.load()
+    tokens, h = x.shape
+    e, _, intermediate = down.shape
+    topk = ids.shape[1]
+    shape = _native.Shape(tokens=tokens, experts=e, topk=topk, hidden=h, intermediate=intermediate,
+                          ids_are_int64=int(ids.dtype == torch.int64),
+                          gate_up_format=_native.WEIGHTS_BF16, down_format=_native.WEIGHTS_BF16,
+                          schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
+                          use_router=int(router_weight is not None))
+    handle = ctypes.c_void_p()
+    _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
+    try:
+        sizes = _native.Workspace()
+        _native.check(lib.b200moe_plan_workspace(handle, ctypes.byref(sizes)))
+        device = x.device
+        r = ids.numel()
+        bf16 = lambda shp: torch.empty(shp, device=device, dtype=torch.bfloat16)
+        int32 = lambda shp: torch.zeros(shp, device=device, dtype=torch.int32)
+        config = config if config is not None else GemmConfig(block_m=max(16, sizes.token_tile))
+        plan = PreparedMoE(
+            x, gate_up, down, ids, routing_weights, bf16((tokens, h)),
+            int32((e,)), int32((e,)), int32((e,)), int32((e + 1,)), int32((r,)),
+            bf16((r, h)), bf16((0, 2 * intermediate)), bf16((r, intermediate)), bf16((r, h)),
+            int32((1,)), config,
+            ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
+            schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile)
+        expected = {"output": plan.output, "counts": plan.counts, "offsets": plan.offsets,
+                    "cursors": plan.cursors, "tasks": plan.tasks, "mapping": plan.mapping, "ranks": plan.ranks,
+                    "grouped_input": plan.grouped_input, "activated": plan.activated,
+                    "down_output": plan.down_output, "status": plan.status, "scratch": plan.scratch}
+        for name, tensor in expected.items():
+            if tensor.numel() * tensor.element_size() < getattr(sizes, name):
+                raise RuntimeError(f"workspace buffer {name} smaller than the library requires")
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
+        buffers = _native.Buffers(
+            x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=None,
+            down=ptr(down), down_scales=None, ids=ptr(ids), routing_weights=ptr(routing_weights),
+            **{name: ptr(tensor) for name, tensor in expected.items()})
+        with torch.cuda.device(device):
+            _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
+    except Exception:
+        lib.b200moe_plan_destroy(handle)
+        raise
+    plan._plan = handle
+    plan._forward = lib.b200moe_forward
+    if tokens:
+        calls = (lib.b200moe_router, lib.b200moe_dispatch, lib.b200moe_gate_up, lib.b200moe_down,
+                 lib.b200moe_combine)
+        plan.launches = tuple(StageLaunch(name, call, handle, device) for name, call in zip(STAGE_NAMES, calls))
+        plan.kernels = {name: plan.schedule for name in STAGE_NAMES}
+    if warm:
+        # populate metadata before any capture; no device value validation here (reference moe.py:243-244)
+        plan.run()
+    return plan
+
+
+def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0):
+    """Drop-in for reference ``prepare_moe`` (moe.py:220-245)."""
+    return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
+                    token_tile=token_tile)

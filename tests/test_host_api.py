@@ -1,0 +1,116 @@
+"""Host-side logic and the C-ABI surface; nothing here needs a GPU."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from llm_gpu_kernels_b200 import _native, moe_full_policy
+from llm_gpu_kernels_b200.gemm import GemmConfig
+from llm_gpu_kernels_b200.moe import prepare_moe
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = "\n".join(p.read_text() for p in (ROOT / "include").glob("*.h"))
+    return sorted(set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _native.load()
+    names = declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert set(names) >= set(_native.EXPORTS)
+    assert lib.b200moe_abi_version() == _native.ABI_VERSION
+
+
+def make_plan(**kw):
+    lib = _native.load()
+    fields = dict(tokens=17, experts=128, topk=8, hidden=2048, intermediate=768)
+    fields.update(kw)
+    shape = _native.Shape(**fields)
+    handle = ctypes.c_void_p()
+    code = lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle))
+    return lib, code, handle
+
+
+def test_plan_create_and_workspace_sizes():
+    lib, code, handle = make_plan()
+    assert code == 0
+    ws = _native.Workspace()
+    assert lib.b200moe_plan_workspace(handle, ctypes.byref(ws)) == 0
+    r = 17 * 8
+    assert ws.output == 17 * 2048 * 2 and ws.mapping == r * 4 and ws.ranks == r * 4
+    assert ws.grouped_input == r * 2048 * 2 and ws.activated == r * 768 * 2 and ws.down_output == r * 2048 * 2
+    assert ws.tasks == 129 * 4 and ws.status == 4
+    assert ws.schedule == _native.SCHEDULE_TCGEN05 and ws.token_tile == 16 and ws.launches == 6
+    lib.b200moe_plan_destroy(handle)
+
+
+@pytest.mark.parametrize("tokens,expect", [(17, 16), (193, 32), (1024, 128), (8192, 128)])
+def test_token_tile_is_shape_only(tokens, expect):
+    lib, code, handle = make_plan(tokens=tokens)
+    ws = _native.Workspace()
+    lib.b200moe_plan_workspace(handle, ctypes.byref(ws))
+    assert ws.token_tile == expect == moe_full_policy.token_tile_for(tokens, 128, 8)
+    lib.b200moe_plan_destroy(handle)
+
+
+@pytest.mark.parametrize("kw", [dict(experts=0), dict(experts=257), dict(topk=0), dict(topk=33), dict(hidden=0),
+                                dict(intermediate=0), dict(tokens=-1), dict(tokens=2**20, topk=32),
+                                dict(token_tile=48), dict(schedule=9)])
+def test_plan_create_rejects(kw):
+    lib, code, _ = make_plan(**kw)
+    assert code == _native.ERR_INVALID
+    assert _native.last_error()
+    with pytest.raises(ValueError):
+        _native.check(code)
+
+
+def test_odd_shapes_take_the_generic_schedule():
+    lib, code, handle = make_plan(hidden=67, intermediate=33, experts=3, topk=2, tokens=9)
+    assert code == 0
+    ws = _native.Workspace()
+    lib.b200moe_plan_workspace(handle, ctypes.byref(ws))
+    assert ws.schedule == _native.SCHEDULE_GENERIC and ws.token_tile == 32
+    lib.b200moe_plan_destroy(handle)
+    _, code, _ = make_plan(hidden=67, intermediate=33, schedule=_native.SCHEDULE_TCGEN05)
+    assert code == _native.ERR_UNSUPPORTED
+
+
+def test_forward_before_bind_is_a_state_error():
+    lib, code, handle = make_plan()
+    assert lib.b200moe_forward(handle, None) == _native.ERR_STATE
+    assert "bind" in _native.last_error()
+    lib.b200moe_plan_destroy(handle)
+
+
+def test_gemm_config_validation():
+    assert GemmConfig().block_m == 32
+    for bad in (dict(block_m=8), dict(block_n=48), dict(warps=2), dict(stages=5)):
+        with pytest.raises(ValueError):
+            GemmConfig(**bad)
+
+
+def test_policy_is_shape_only():
+    cfg, bucket = moe_full_policy.select(17, 128, 8, 2048, 768)
+    assert (cfg.block_m, bucket) == (16, "small")
+    assert moe_full_policy.select(1024, 128, 8, 2048, 768)[1] == "medium"
+    assert moe_full_policy.select(4096, 128, 8, 2048, 768) == (GemmConfig(block_m=128), "large")
+    assert moe_full_policy.select(0, 128, 8, 2048, 768)[1] == "small"
+    with pytest.raises(ValueError):
+        moe_full_policy.select(-1, 128, 8, 2048, 768)
+
+
+def test_prepare_rejects_host_tensors_without_touching_a_gpu():
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    gu = torch.zeros(2, 128, 64, dtype=torch.bfloat16)
+    dn = torch.zeros(2, 64, 64, dtype=torch.bfloat16)
+    ids = torch.zeros(4, 2, dtype=torch.int32)
+    rw = torch.zeros(4, 2)
+    with pytest.raises(ValueError, match="contiguous CUDA BF16"):
+        prepare_moe(x, gu, dn, ids, rw)

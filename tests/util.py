@@ -1,0 +1,61 @@
+"""Seeded input generators shared by the tests (CPU generator, then moved).
+
+Route patterns restate reference moe_benchmark.py:43-64 (random / duplicate /
+all_hot / hot); tensors follow moe_benchmark.py:67-82 (FP32 draws cast to
+BF16, un-normalised uniform routing weights) with an optional weight scale.
+"""
+import hashlib
+
+import torch
+
+
+def digest(t):
+    t = t.detach().cpu().contiguous()
+    h = hashlib.sha256(str((str(t.dtype), tuple(t.shape))).encode())
+    h.update(t.view(torch.uint8).numpy().tobytes())
+    return h.hexdigest()
+
+
+def make_ids(tokens, experts, topk, pattern, generator):
+    if tokens == 0:
+        return torch.empty((0, topk), dtype=torch.int64)
+    if pattern == "duplicate":
+        base = torch.arange(tokens)[:, None] % experts
+        slots = torch.arange(topk)[None, :]
+        return (base + slots // 2) % experts
+    if pattern == "all_hot":
+        return torch.zeros((tokens, topk), dtype=torch.int64)
+    if pattern == "last_hot":
+        return torch.full((tokens, topk), experts - 1, dtype=torch.int64)
+    if pattern == "hot":
+        hot = min(experts, max(topk, experts // 8))
+        chosen = torch.randperm(experts, generator=generator)[:hot]
+        return chosen[torch.rand((tokens, hot), generator=generator).topk(topk, dim=1).indices]
+    if pattern == "balanced":
+        return (torch.arange(tokens * topk).reshape(tokens, topk)) % experts
+    if pattern == "random":
+        return torch.rand((tokens, experts), generator=generator).topk(topk, dim=1).indices
+    raise ValueError(pattern)
+
+
+def make_inputs(tokens, experts, topk, hidden, inter, *, pattern="random", seed=0, id_dtype=torch.int32,
+                wscale=1.0, signed=False, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((tokens, hidden), generator=g).bfloat16()
+    gate_up = (wscale * torch.randn((experts, 2 * inter, hidden), generator=g)).bfloat16()
+    down = (wscale * torch.randn((experts, hidden, inter), generator=g)).bfloat16()
+    ids = make_ids(tokens, experts, topk, pattern, g).to(id_dtype)
+    rw = torch.rand((tokens, topk), generator=g)
+    if signed:
+        rw = rw * 2 - 1
+    return tuple(t.to(device) for t in (x, gate_up, down, ids, rw))
+
+
+def seeded_layer(seed, tokens, hidden, inter, experts, wscale=0.02, device="cpu"):
+    """Draw order: router weight, gate_up, down, x (FP32 draws cast to BF16)."""
+    g = torch.Generator().manual_seed(seed)
+    wr = (wscale * torch.randn(experts, hidden, generator=g)).bfloat16()
+    gate_up = (wscale * torch.randn(experts, 2 * inter, hidden, generator=g)).bfloat16()
+    down = (wscale * torch.randn(experts, hidden, inter, generator=g)).bfloat16()
+    x = torch.randn(tokens, hidden, generator=g).bfloat16()
+    return tuple(t.to(device) for t in (wr, gate_up, down, x))
