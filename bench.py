@@ -255,6 +255,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--tokens", type=int, default=1024, help="headline batch size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-headline", action="store_true", help="time only --tokens (short profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -277,6 +278,8 @@ def main():
     wr, gate_up, down, g = seeded_weights(**QWEN)
     weights_cpu = (wr, gate_up, down)
     xs = {t: torch.randn(t, QWEN["hidden"], generator=g).bfloat16() for t in TOKENS}
+    if args.only_headline:
+        xs = {t: v for t, v in xs.items() if t == args.tokens}
     if args.tokens not in xs:
         xs[args.tokens] = torch.randn(args.tokens, QWEN["hidden"], generator=g).bfloat16()
     wr_d, gate_up_d, down_d = (t.to(dev) for t in weights_cpu)
