@@ -188,7 +188,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.activated = R * I * 2;
   w.down_output = R * H * 2;
   w.status = 4;
-  w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks) * 4);
+  w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 1) * 4);
   w.token_tile = tile;
   w.schedule = schedule;
   w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + 6;
@@ -256,7 +256,15 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
         }
   }
   p->buf = *b;
-  if (s.tokens > 0 && s.use_router) {
+  p->router_tc = false;
+  if (s.tokens > 0 && s.use_router && p->schedule == B200MOE_SCHEDULE_TCGEN05 &&
+      (reinterpret_cast<uintptr_t>(b->x) | reinterpret_cast<uintptr_t>(b->router_weight)) % 16 == 0) {
+    const uint32_t e_pad = static_cast<uint32_t>((s.experts + 15) / 16 * 16);
+    if ((rc = encode_2d(&p->tm_x, b->x, s.tokens, s.hidden, 128, false))) return rc;
+    if ((rc = encode_2d(&p->tm_router_w, b->router_weight, s.experts, s.hidden, e_pad, false))) return rc;
+    if ((rc = configure_router_tc(*p))) return rc;
+    p->router_tc = true;
+  } else if (s.tokens > 0 && s.use_router) {
     const size_t smem = router_smem_bytes(s.hidden, s.experts);
     if (smem > 48 * 1024) {
       rc = check_cuda(router_opt_in_smem(smem), "router shared-memory opt-in");
@@ -285,7 +293,8 @@ int b200moe_router(B200MoePlan* p, void* stream) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0 || !p->shape.use_router) return B200MOE_OK;
-  return check_cuda(launch_router(*p, static_cast<cudaStream_t>(stream)), "router launch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return check_cuda(p->router_tc ? launch_router_tc(*p, s) : launch_router(*p, s), "router launch");
 }
 
 int b200moe_dispatch(B200MoePlan* p, void* stream) {

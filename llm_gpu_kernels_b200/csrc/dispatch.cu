@@ -30,7 +30,7 @@ constexpr int kWarps = kDispatchWarps;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxExperts = 256;
 
-// scratch layout: int32 hist[partitions][E], then int32 flags[blocks]
+// scratch layout: int32 hist[partitions][E], int32 flags[blocks], int32 router_flag
 template <typename IdT>
 __global__ void __launch_bounds__(kThreads)
 dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
@@ -77,7 +77,8 @@ dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
 __global__ void __launch_bounds__(kMaxExperts)
 dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int* __restrict__ counts,
                      int* __restrict__ offsets, int* __restrict__ cursors, int* __restrict__ tasks,
-                     int* __restrict__ status, int E, int partitions, int blocks, int token_tile) {
+                     int* __restrict__ status, int* __restrict__ router_flag, int E, int partitions, int blocks,
+                     int token_tile) {
   __shared__ int s_count[kMaxExperts];
   __shared__ int s_tiles[kMaxExperts];
   __shared__ int s_flags;
@@ -109,7 +110,10 @@ dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int*
     tasks[e] = toff;
     if (e == E - 1) tasks[E] = toff + s_tiles[e];
   }
-  if (e == 0) *status = s_flags;
+  if (e == 0) {  // the status word restarts every forward; fold in what the router raised
+    *status = s_flags | *router_flag;
+    *router_flag = 0;
+  }
 }
 
 template <typename IdT>
@@ -165,8 +169,8 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   }
   dispatch_scan_kernel<<<1, kMaxExperts, 0, s>>>(
       hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
-      static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status), E,
-      p.partitions, blocks, p.token_tile);
+      static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status),
+      hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile);
   const int pblocks = (R + kWarps - 1) / kWarps;
   auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
   auto* grouped = static_cast<__nv_bfloat16*>(p.buf.grouped_input);

@@ -29,9 +29,12 @@
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
+#include "sm100_ptx.cuh"
 
 namespace b200moe {
 namespace {
+
+using namespace ptx;
 
 constexpr int kBlockK = 64;                    // bf16 per k-block: 128 bytes = one swizzle row
 constexpr int kTileM = 128;                    // output channels per tile (UMMA M)
@@ -42,7 +45,6 @@ constexpr int kMaxExperts = 256;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
 constexpr int kSmemLimit = 232448;             // 227 KB opt-in limit per CTA
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // 1 s per wait
 
 struct Ctrl {
   uint64_t full[kMaxStages];
@@ -57,90 +59,6 @@ struct Ctrl {
   int counts[kMaxExperts];
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false when the wait was given up (by this thread on
-// expiry, or because another role of the CTA already gave up).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* c, int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_timer();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0) {
-      if (*reinterpret_cast<volatile int*>(&c->abort)) return false;
-      if (global_timer() - start > kWaitLimitNs) {
-        *reinterpret_cast<volatile int*>(&c->abort) = 1;
-        atomicOr(status, B200MOE_STATUS_TIMEOUT);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
-                                            uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// K-major operand tile written by TMA with 128-byte swizzle: rows of 128 bytes,
-// 8-row groups 1024 bytes apart (SBO), version 1 (sm_100), layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// kind::f16, BF16 x BF16 -> FP32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(kTileM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct Tile {
   int expert, ct, row0, rows, n_eff;
@@ -204,13 +122,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     }
     mbar_init(&c->drain, 1);
     c->abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&c->tmem_base)), "r"(tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&c->tmem_base, tmem_cols);
   }
   tc_fence_before();
   __syncthreads();
@@ -224,10 +139,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (warp == 0) {
     if (lane == 0) {
       // ---------------------------------------------------------------- TMA producer
-      uint64_t pol_w, pol_act;
-      if (stream_weights) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_w));
-      else asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_w));
-      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_act));
+      const uint64_t pol_w = stream_weights ? policy_evict_first() : policy_evict_last();
+      const uint64_t pol_act = policy_evict_last();
       int stage = 0;
       uint32_t phase = 0;
       long long issued = 0;
@@ -236,7 +149,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         const Tile t = decode_tile(c, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&c->empty[stage], phase ^ 1u, c, status)) { ok = false; break; }
+          if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) { ok = false; break; }
           unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
           mbar_expect_tx(&c->full[stage], stage_bytes);
           tma_load_2d(st, &tm_w, &c->full[stage], kb * kBlockK, w_row, pol_w);
@@ -252,10 +165,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       for (long long i = first; i < issued; ++i) {
         const int s = static_cast<int>(i % num_stages);
         const uint32_t ph = static_cast<uint32_t>((i / num_stages) & 1);
-        const unsigned long long start = global_timer();
-        while (!mbar_try_wait(&c->full[s], ph)) {
-          if (global_timer() - start > kWaitLimitNs) { atomicOr(status, B200MOE_STATUS_TIMEOUT); break; }
-        }
+        if (!mbar_wait_plain(&c->full[s], ph)) { atomicOr(status, B200MOE_STATUS_TIMEOUT); break; }
       }
     }
   } else if (warp == 1) {
@@ -266,13 +176,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const Tile t = decode_tile(c, item, E, n_ct, token_tile);
-        const uint32_t idesc = umma_idesc(t.n_eff);
-        if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, c, status)) { ok = false; break; }
+        const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
+        if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
         const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&c->full[stage], phase, c, status)) { ok = false; break; }
+          if (!mbar_wait(&c->full[stage], phase, &c->abort, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t w_addr = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
           const uint32_t a_addr = w_addr + kWBytes;
@@ -292,10 +202,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       }
       if (!ok) {  // gave up: let the MMAs already issued finish before TMEM is freed
         umma_commit(&c->drain);
-        const unsigned long long start = global_timer();
-        while (!mbar_try_wait(&c->drain, 0)) {
-          if (global_timer() - start > kWaitLimitNs) break;
-        }
+        mbar_wait_plain(&c->drain, 0);
       }
     }
   } else {
@@ -306,7 +213,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const Tile t = decode_tile(c, item, E, n_ct, token_tile);
       // warp-uniform outcome: the TMEM loads below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, c, status))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const int channel = t.ct * kTileM + quarter * 32 + lane;
       const bool ch_ok = channel < n_out;
@@ -336,7 +243,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 

@@ -23,6 +23,11 @@ struct B200MoePlan {
   CUtensorMap tm_grouped{};     // [R, H] bf16, box 64 x token_tile
   CUtensorMap tm_down_w{};      // [E*H, I] bf16, box 64 x 128
   CUtensorMap tm_activated{};   // [R, I] bf16, box 64 x token_tile
+  // router on the tensor cores (tcgen05 schedule with a router)
+  bool router_tc = false;
+  CUtensorMap tm_x{};           // [T, H] bf16, box 64 x 128
+  CUtensorMap tm_router_w{};    // [E, H] bf16, box 64 x round_up(E,16)
+  int router_smem = 0, router_stages = 0;
   int gemm_smem_gate_up = 0, gemm_stages_gate_up = 0;
   int gemm_smem_down = 0, gemm_stages_down = 0;
 };
@@ -33,6 +38,7 @@ void set_error(const char* fmt, ...);
 
 // Each returns a cudaError_t from the launch (cudaPeekAtLastError), never synchronises.
 cudaError_t launch_router(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_router_tc(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_gate_up_generic(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_generic(const B200MoePlan& p, cudaStream_t s);
@@ -45,6 +51,14 @@ cudaError_t router_opt_in_smem(size_t bytes);
 
 // One-time per-plan set-up of the tcgen05 kernels (smem opt-in, stage counts).
 int configure_tc(B200MoePlan& p);
+int configure_router_tc(B200MoePlan& p);
+
+// The router raises its timeout flag in a scratch word (the dispatch folds it into the
+// status word, which it resets every forward): int32 index of that word inside `scratch`.
+inline size_t router_flag_index(const B200MoePlan& p) {
+  const int blocks = (p.partitions + 7) / 8;
+  return static_cast<size_t>(p.partitions) * p.shape.experts + blocks;
+}
 
 constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
 constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels

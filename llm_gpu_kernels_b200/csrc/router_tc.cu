@@ -1,0 +1,213 @@
+// Router on the tensor cores: logits[token][expert] = x . Wr^T as one tcgen05
+// GEMM per 128-token tile (tokens on the TMEM lanes, experts on the columns), then
+// softmax + top-k + renormalisation by the thread that owns the token's lane -
+// no cross-thread exchange: the whole row of logits is that lane's TMEM row.
+//
+// Formula: scripts/capture_qwen3_moe_layer0.py:583-586 of the reference (FP32
+// softmax, top-k, divide by the sum of the k). The k experts are taken in
+// descending logit order (softmax is monotonic), ties to the lowest index;
+// weights are exp(l - max) / sum over all experts, renormalised over the k.
+// Columns >= E (zero-filled by TMA) and lanes >= T are masked.
+#include <cuda_bf16.h>
+#include "plan.h"
+#include "sm100_ptx.cuh"
+
+namespace b200moe {
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+constexpr int kMaxStages = 8;
+constexpr int kTileTokens = 128;   // UMMA M
+constexpr int kBlockK = 64;
+constexpr int kCtrlBytes = 1024;
+constexpr int kSmemLimit = 232448;
+
+struct Ctrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+template <typename IdT>
+__global__ void __launch_bounds__(kThreads, 1)
+router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_wr,
+                 IdT* __restrict__ ids, float* __restrict__ rw, int* __restrict__ status, int T, int E, int H,
+                 int K, int e_pad, int num_stages) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t stage_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
+  unsigned char* stages = smem_raw + stage_off;
+  constexpr uint32_t kXBytes = kTileTokens * 128;
+  const uint32_t stage_bytes = kXBytes + static_cast<uint32_t>(e_pad) * 128u;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(e_pad)) tmem_cols <<= 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * kTileTokens;
+  const int num_kb = (H + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < num_stages; ++s) {
+      mbar_init(&c->full[s], 1);
+      mbar_init(&c->empty[s], 1);
+    }
+    mbar_init(&c->tmem_full, 1);
+    c->abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_last();  // x is read again by dispatch, Wr by every tile
+      int stage = 0, issued = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) break;
+        unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
+        mbar_expect_tx(&c->full[stage], stage_bytes);
+        tma_load_2d(st, &tm_x, &c->full[stage], kb * kBlockK, t0, pol);
+        tma_load_2d(st + kXBytes, &tm_wr, &c->full[stage], kb * kBlockK, 0, pol);
+        ++issued;
+        if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+      }
+      for (int i = issued > num_stages ? issued - num_stages : 0; i < issued; ++i) {  // no copy left in flight
+        if (!mbar_wait_plain(&c->full[i % num_stages], static_cast<uint32_t>((i / num_stages) & 1))) {
+          atomicOr(status, B200MOE_STATUS_TIMEOUT);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kTileTokens, e_pad);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&c->full[stage], phase, &c->abort, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t x_addr = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
+        const uint32_t w_addr = x_addr + kXBytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma(tmem_base, umma_desc(x_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(&c->empty[stage]);
+        if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+      }
+      umma_commit(&c->tmem_full);  // also the drain point when the loop gave up
+      if (!ok) mbar_wait_plain(&c->tmem_full, 0);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const bool ready = __all_sync(0xffffffffu, mbar_wait(&c->tmem_full, 0, &c->abort, status));
+    if (ready) {
+      tc_fence_after();
+      const int token = t0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint32_t v[16];
+      float m = -INFINITY;
+      for (int c0 = 0; c0 < e_pad; c0 += 16) {
+        tmem_ld16(taddr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < E) m = fmaxf(m, __uint_as_float(v[j]));
+      }
+      float sum = 0.0f;
+      for (int c0 = 0; c0 < e_pad; c0 += 16) {
+        tmem_ld16(taddr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < E) sum += expf(__uint_as_float(v[j]) - m);
+      }
+      float prev_v = INFINITY, total = 0.0f;
+      int prev_e = -1;
+      const bool live = token < T;
+      IdT* my_ids = ids + static_cast<size_t>(live ? token : 0) * K;
+      float* my_rw = rw + static_cast<size_t>(live ? token : 0) * K;
+      for (int k = 0; k < K; ++k) {
+        float best_v = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int c0 = 0; c0 < e_pad; c0 += 16) {
+          tmem_ld16(taddr + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float l = __uint_as_float(v[j]);
+            const int e = c0 + j;
+            const bool after_prev = l < prev_v || (l == prev_v && e > prev_e);
+            if (e < E && after_prev && (l > best_v || best_e == 0x7fffffff)) { best_v = l; best_e = e; }
+          }
+        }
+        if (best_e >= E) { best_e = min(k, E - 1); best_v = -INFINITY; }  // NaN logits: stay in range
+        prev_v = best_v;
+        prev_e = best_e;
+        const float p = expf(best_v - m) / sum;
+        total += p;
+        if (live) {
+          my_ids[k] = static_cast<IdT>(best_e);
+          my_rw[k] = p;
+        }
+      }
+      if (live)
+        for (int k = 0; k < K; ++k) my_rw[k] = my_rw[k] / total;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+}  // namespace
+
+int configure_router_tc(B200MoePlan& p) {
+  const int e_pad = (p.shape.experts + 15) / 16 * 16;
+  const int stage = kTileTokens * 128 + e_pad * 128;
+  int stages = (kSmemLimit - kCtrlBytes - 1024) / stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  p.router_stages = stages;
+  p.router_smem = kCtrlBytes + 1024 + stages * stage;
+  cudaError_t e = cudaFuncSetAttribute(router_tc_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(router_tc_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(router shared memory) failed: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+cudaError_t launch_router_tc(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  const int grid = (sh.tokens + kTileTokens - 1) / kTileTokens;
+  const int e_pad = (sh.experts + 15) / 16 * 16;
+  auto* rw = static_cast<float*>(p.buf.routing_weights);
+  int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
+  if (sh.ids_are_int64) {
+    router_tc_kernel<long long><<<grid, kThreads, p.router_smem, s>>>(
+        p.tm_x, p.tm_router_w, static_cast<long long*>(p.buf.ids), rw, status, sh.tokens, sh.experts, sh.hidden,
+        sh.topk, e_pad, p.router_stages);
+  } else {
+    router_tc_kernel<int><<<grid, kThreads, p.router_smem, s>>>(
+        p.tm_x, p.tm_router_w, static_cast<int*>(p.buf.ids), rw, status, sh.tokens, sh.experts, sh.hidden, sh.topk,
+        e_pad, p.router_stages);
+  }
+  return cudaPeekAtLastError();
+}
+
+}  // namespace b200moe
