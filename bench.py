@@ -199,7 +199,7 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx):
         "schedule": base.schedule, "alg_flops": flops, "alg_bytes": nbytes,
         "layer_hbm_gbs": nbytes / (graph_ms * 1e-3) / 1e9, "layer_roofline_frac": t_roof_ms / graph_ms,
         "stage_ms": stage_ms, "gate_up_alg_bytes": gate_up_bytes, "gate_up_gbs": gate_up_gbs,
-        "h2d_bytes": tokens * h * 2, "d2h_bytes": tokens * h * 2, "launches": 6 + 1,
+        "h2d_bytes": tokens * h * 2, "d2h_bytes": tokens * h * 2, "launches": base.kernel_launches,
     }
 
 

@@ -170,9 +170,16 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   p->routes = static_cast<int>(r);
   p->schedule = schedule;
   p->token_tile = tile;
-  const int per_warp = round_up(static_cast<int>((r + 511) / 512), 32);
-  p->warp_routes = per_warp < 128 ? 128 : per_warp;
-  p->partitions = static_cast<int>((r + p->warp_routes - 1) / p->warp_routes);
+  p->dispatch_fused = r <= kFusedRoutes;
+  if (p->dispatch_fused) {  // 32 warps of one block share the routes
+    const int per_warp = round_up(static_cast<int>((r + 31) / 32), 32);
+    p->warp_routes = per_warp < 32 ? 32 : per_warp;
+    p->partitions = 32;
+  } else {
+    const int per_warp = round_up(static_cast<int>((r + 511) / 512), 32);
+    p->warp_routes = per_warp < 128 ? 128 : per_warp;
+    p->partitions = static_cast<int>((r + p->warp_routes - 1) / p->warp_routes);
+  }
   const int blocks = (p->partitions + kDispatchWarps - 1) / kDispatchWarps;
 
   B200MoeWorkspace& w = p->ws;
@@ -191,7 +198,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 1) * 4);
   w.token_tile = tile;
   w.schedule = schedule;
-  w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + 6;
+  w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + 3;
   *out = p;
   return B200MOE_OK;
 }

@@ -11,7 +11,7 @@
 namespace b200moe {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 64;  // small blocks: T * H/512 of them even for a handful of tokens
 
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
@@ -29,16 +29,26 @@ combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict
     const int h = (blockIdx.y * kThreads + threadIdx.x) * 8;
     if (h >= H) return;
     float acc[8] = {};
-    for (int slot = 0; slot < K; ++slot) {
-      const int pos = s_pos[slot];
-      if (pos < 0) continue;
-      const float w = s_w[slot];
-      const uint4 p = *reinterpret_cast<const uint4*>(down_out + static_cast<size_t>(pos) * H + h);
-      const uint32_t u[4] = {p.x, p.y, p.z, p.w};
+    for (int s0 = 0; s0 < K; s0 += 8) {  // issue the (independent) row loads first, then add in slot order
+      uint4 v[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
-        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xffff0000u), w));
+      for (int j = 0; j < 8; ++j) {
+        const int slot = s0 + j;
+        const int pos = slot < K ? s_pos[slot] : -1;
+        v[j] = pos >= 0 ? *reinterpret_cast<const uint4*>(down_out + static_cast<size_t>(pos) * H + h)
+                        : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int slot = s0 + j;
+        if (slot >= K || s_pos[slot] < 0) continue;
+        const float w = s_w[slot];
+        const uint32_t u[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(__uint_as_float(u[i] << 16), w));
+          acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(__uint_as_float(u[i] & 0xffff0000u), w));
+        }
       }
     }
     uint4 o;

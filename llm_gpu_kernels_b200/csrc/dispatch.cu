@@ -9,7 +9,9 @@
 // expert, which is the stable order of argsort(ids, stable=True). No global
 // atomics are used, so counts / offsets / ranks / mapping are bit-reproducible.
 //
-// Three kernels:
+// Up to kFusedRoutes routes one 1024-thread block does count + scan + final
+// ranks / mapping in a single launch (warp histograms stay in shared memory)
+// and a second kernel copies the rows. Above that, three kernels:
 //  count   - every warp owns `warp_routes` consecutive routes and walks them 32
 //            at a time in order: __match_any_sync gives the lanes with the same
 //            expert, so rank-in-partition = running warp histogram + number of
@@ -74,45 +76,165 @@ dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
   if (threadIdx.x == 0) flags[blockIdx.x] = block_flags;
 }
 
+// Exclusive prefix over the experts of (count, tiles) for the first 256 threads of a block.
+// Every thread of the block must call it (it synchronises); `scratch` holds 2 x 8 ints.
+__device__ __forceinline__ void expert_prefix(int count, int tiles, int* scratch, int* count_excl, int* tiles_excl,
+                                              int* tiles_total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int c = count, t = tiles;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int oc = __shfl_up_sync(0xffffffffu, c, o), ot = __shfl_up_sync(0xffffffffu, t, o);
+    if (lane >= o) { c += oc; t += ot; }
+  }
+  if (warp < 8 && lane == 31) { scratch[warp] = c; scratch[8 + warp] = t; }
+  __syncthreads();
+  int cb = 0, tb = 0, tt = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) { cb += scratch[w]; tb += scratch[8 + w]; }
+    tt += scratch[8 + w];
+  }
+  *count_excl = c - count + cb;
+  *tiles_excl = t - tiles + tb;
+  *tiles_total = tt;
+}
+
 __global__ void __launch_bounds__(kMaxExperts)
 dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int* __restrict__ counts,
                      int* __restrict__ offsets, int* __restrict__ cursors, int* __restrict__ tasks,
                      int* __restrict__ status, int* __restrict__ router_flag, int E, int partitions, int blocks,
                      int token_tile) {
-  __shared__ int s_count[kMaxExperts];
-  __shared__ int s_tiles[kMaxExperts];
+  __shared__ int s_scan[16];
   __shared__ int s_flags;
   const int e = threadIdx.x;
   if (e == 0) s_flags = 0;
   __syncthreads();
   int total = 0;
   if (e < E) {
-    for (int p = 0; p < partitions; ++p) {
-      const size_t i = static_cast<size_t>(p) * E + e;
-      const int c = hist[i];
-      hist[i] = total;
-      total += c;
+    for (int p0 = 0; p0 < partitions; p0 += 8) {  // loads first, then the dependent running sum
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = p0 + j < partitions ? hist[static_cast<size_t>(p0 + j) * E + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (p0 + j < partitions) hist[static_cast<size_t>(p0 + j) * E + e] = total;
+        total += c[j];
+      }
     }
   }
   int f = 0;
   for (int b = e; b < blocks; b += blockDim.x) f |= flags[b];
   if (f) atomicOr(&s_flags, f);
-  s_count[e] = e < E ? total : 0;
-  s_tiles[e] = e < E ? (total + token_tile - 1) / token_tile : 0;
-  __syncthreads();
-  // E <= 256: a serial exclusive prefix per thread over shared memory is cheap and exact
+  const int tiles = e < E ? (total + token_tile - 1) / token_tile : 0;
+  int off, toff, ttotal;
+  expert_prefix(e < E ? total : 0, tiles, s_scan, &off, &toff, &ttotal);
   if (e < E) {
-    int off = 0, toff = 0;
-    for (int j = 0; j < e; ++j) { off += s_count[j]; toff += s_tiles[j]; }
     counts[e] = total;
     offsets[e] = off;
     cursors[e] = 0;
     tasks[e] = toff;
-    if (e == E - 1) tasks[E] = toff + s_tiles[e];
+    if (e == E - 1) tasks[E] = ttotal;
   }
   if (e == 0) {  // the status word restarts every forward; fold in what the router raised
     *status = s_flags | *router_flag;
     *router_flag = 0;
+  }
+}
+
+// One block does the whole dispatch metadata for up to kFusedRoutes routes.
+template <typename IdT>
+__global__ void __launch_bounds__(1024)
+dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
+                      int* __restrict__ mapping, int* __restrict__ counts, int* __restrict__ offsets,
+                      int* __restrict__ cursors, int* __restrict__ tasks, int* __restrict__ status,
+                      int* __restrict__ router_flag, int R, int E, int warp_routes, int token_tile) {
+  __shared__ int warp_hist[32][kMaxExperts];
+  __shared__ int s_off[kMaxExperts];
+  __shared__ int s_scan[16];
+  __shared__ int s_flags;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) s_flags = 0;
+  for (int e = lane; e < E; e += 32) warp_hist[warp][e] = 0;
+  __syncthreads();
+  const int begin = min(R, warp * warp_routes), end = min(R, begin + warp_routes);
+  int my_flags = 0;
+  for (int base = begin; base < end; base += 32) {
+    const int q = base + lane;
+    const bool in = q < end;
+    const long long id = in ? static_cast<long long>(ids[q]) : -1;
+    const float w = in ? rw[q] : 0.0f;
+    const bool valid = in && id >= 0 && id < E;
+    if (in && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
+    if (in && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;
+    const int key = valid ? static_cast<int>(id) : E;
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int below = __popc(peers & ((1u << lane) - 1u));
+    const int rank = valid ? warp_hist[warp][key] + below : -1;
+    __syncwarp();
+    if (valid && below == 0) warp_hist[warp][key] += __popc(peers);
+    __syncwarp();
+    if (in) ranks[q] = rank;
+  }
+  if (my_flags) atomicOr(&s_flags, my_flags);
+  __syncthreads();
+  const int e = threadIdx.x;
+  int total = 0;
+  if (e < E) {
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_hist[w][e];
+      warp_hist[w][e] = total;  // base rank of warp w's partition inside expert e
+      total += c;
+    }
+  }
+  const int tiles = e < E ? (total + token_tile - 1) / token_tile : 0;
+  int off, toff, ttotal;
+  expert_prefix(e < E ? total : 0, tiles, s_scan, &off, &toff, &ttotal);
+  if (e < E) {
+    counts[e] = total;
+    offsets[e] = off;
+    cursors[e] = 0;
+    tasks[e] = toff;
+    s_off[e] = off;
+    if (e == E - 1) tasks[E] = ttotal;
+  }
+  if (e == 0) {
+    *status = s_flags | *router_flag;
+    *router_flag = 0;
+  }
+  __syncthreads();
+  for (int base = begin; base < end; base += 32) {
+    const int q = base + lane;
+    if (q >= end) continue;
+    const long long id = static_cast<long long>(ids[q]);
+    int rank = -1, pos = -1;
+    if (id >= 0 && id < E) {
+      rank = ranks[q] + warp_hist[warp][id];  // ranks[q] was written by this same thread above
+      pos = s_off[id] + rank;
+    }
+    ranks[q] = rank;
+    mapping[q] = pos;
+  }
+}
+
+// Row copy for the fused path: grouped_input[mapping[q], :] = x[q / K, :], one warp per route.
+__global__ void __launch_bounds__(kThreads)
+dispatch_copy_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ mapping,
+                     __nv_bfloat16* __restrict__ grouped, int R, int H, int K) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = blockIdx.x * kWarps + warp;
+  if (q >= R) return;
+  const int pos = mapping[q];
+  if (pos < 0) return;
+  const __nv_bfloat16* src = x + static_cast<size_t>(q / K) * H;
+  __nv_bfloat16* dst = grouped + static_cast<size_t>(pos) * H;
+  if ((H & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grouped)) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = lane; i < H / 8; i += 32) d4[i] = s4[i];
+  } else {
+    for (int i = lane; i < H; i += 32) dst[i] = src[i];
   }
 }
 
@@ -160,6 +282,28 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   int* flags = hist + static_cast<size_t>(p.partitions) * E;
   int* ranks = static_cast<int*>(p.buf.ranks);
   auto* rw = static_cast<const float*>(p.buf.routing_weights);
+  if (p.dispatch_fused) {
+    int* router_flag = hist + router_flag_index(p);
+    auto* counts = static_cast<int*>(p.buf.counts);
+    auto* offsets = static_cast<int*>(p.buf.offsets);
+    auto* cursors = static_cast<int*>(p.buf.cursors);
+    auto* tasks = static_cast<int*>(p.buf.tasks);
+    auto* status = static_cast<int*>(p.buf.status);
+    auto* mapping = static_cast<int*>(p.buf.mapping);
+    if (sh.ids_are_int64) {
+      dispatch_fused_kernel<long long><<<1, 1024, 0, s>>>(static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
+                                                          counts, offsets, cursors, tasks, status, router_flag, R, E,
+                                                          p.warp_routes, p.token_tile);
+    } else {
+      dispatch_fused_kernel<int><<<1, 1024, 0, s>>>(static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
+                                                    offsets, cursors, tasks, status, router_flag, R, E, p.warp_routes,
+                                                    p.token_tile);
+    }
+    dispatch_copy_kernel<<<(R + kWarps - 1) / kWarps, kThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(p.buf.x), mapping, static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
+        sh.hidden, sh.topk);
+    return cudaPeekAtLastError();
+  }
   if (sh.ids_are_int64) {
     dispatch_count_kernel<long long><<<blocks, kThreads, 0, s>>>(
         static_cast<const long long*>(p.buf.ids), rw, ranks, hist, flags, R, E, p.warp_routes, p.partitions);

@@ -18,6 +18,7 @@ struct B200MoePlan {
   // dispatch partition: each warp ranks `warp_routes` consecutive routes
   int warp_routes = 0;
   int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
+  bool dispatch_fused = false;  // one-block count + scan + mapping (R <= kFusedRoutes)
   // TMA descriptors (tcgen05 schedule)
   CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128
   CUtensorMap tm_grouped{};     // [R, H] bf16, box 64 x token_tile
@@ -61,6 +62,7 @@ inline size_t router_flag_index(const B200MoePlan& p) {
 }
 
 constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
+constexpr int kFusedRoutes = 16384;  // up to here one 1024-thread block builds the dispatch metadata
 constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels
 
 }  // namespace b200moe

@@ -83,6 +83,7 @@ class PreparedMoE:
     schedule: str = ""
     token_tile: int = 0
     launches: tuple = ()
+    kernel_launches: int = 0  # kernels one run() enqueues
     _plan: object = field(default=None, repr=False)
     _forward: object = field(default=None, repr=False)
 
@@ -199,7 +200,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
             bf16((r, h)), bf16((0, 2 * intermediate)), bf16((r, intermediate)), bf16((r, h)),
             int32((1,)), config,
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
-            schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile)
+            schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
+            kernel_launches=sizes.launches)
         expected = {"output": plan.output, "counts": plan.counts, "offsets": plan.offsets,
                     "cursors": plan.cursors, "tasks": plan.tasks, "mapping": plan.mapping, "ranks": plan.ranks,
                     "grouped_input": plan.grouped_input, "activated": plan.activated,

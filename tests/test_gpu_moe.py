@@ -132,6 +132,48 @@ def test_qwen_shape_full_layer(dev, tokens):
         assert torch.equal(p.run(), first)
 
 
+ROUTER = [
+    (64, 8, 2, 256, 128, None),       # tensor-core router, E padded to 16 columns
+    (300, 20, 5, 192, 64, None),      # three token tiles, E = 20 -> 32 columns, ragged last tile
+    (130, 256, 32, 128, 64, None),    # widest supported: E = 256, K = 32
+    (40, 16, 4, 128, 64, "generic"),  # CUDA-core router on an aligned shape
+    (9, 3, 3, 67, 33, None),          # odd H: CUDA-core router and GEMMs
+    (5, 130, 8, 96, 72, None),
+]
+
+
+@pytest.mark.parametrize("t,e,k,h,i,schedule", ROUTER)
+def test_router_shapes(dev, t, e, k, h, i, schedule):
+    from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    wr, gate_up, down, x = seeded_layer(3 + t, t, h, i, e, wscale=0.05)
+    for id_dtype in (torch.int32, torch.int64):
+        ids = torch.zeros(t, k, dtype=id_dtype, device=dev)
+        rw = torch.zeros(t, k, dtype=torch.float32, device=dev)
+        p = prepare_ranked_moe_launcher(x.to(dev), gate_up.to(dev), down.to(dev), ids, rw,
+                                        router_weight=wr.to(dev), schedule=schedule)
+        out = p.run()
+        torch.cuda.synchronize()
+        p.check_inputs()
+        _, _, probs = O.router_oracle(x, wr, k)
+        ok, msg = O.router_agrees(ids.cpu(), rw.cpu(), probs, k)
+        assert ok, msg
+        check_dispatch(p.base, x, ids.cpu(), e)
+        check_output(out, (x, gate_up, down, ids.cpu(), rw.cpu()))
+
+
+@pytest.mark.parametrize("pattern", ["random", "hot", "all_hot"])
+def test_large_route_count_multi_block_dispatch(dev, pattern):
+    """R = 20000 routes takes the multi-block count / scan / permute path."""
+    cpu = make_inputs(2500, 64, 8, 64, 64, pattern=pattern, seed=77, wscale=0.2, signed=True)
+    gpu = tuple(a.to(dev) for a in cpu)
+    p = prep()(*gpu)
+    out = p.run()
+    torch.cuda.synchronize()
+    p.check_inputs()
+    check_dispatch(p.base, cpu[0], cpu[3], 64)
+    check_output(out, cpu)
+
+
 def test_tiny_layer_golden(dev, golden_dir):
     """BASELINE config 1 against the reference's own output on the same seeded inputs."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
