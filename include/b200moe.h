@@ -150,6 +150,53 @@ int b200moe_gate_up(B200MoePlan* plan, void* cuda_stream);
 int b200moe_down(B200MoePlan* plan, void* cuda_stream);
 int b200moe_combine(B200MoePlan* plan, void* cuda_stream);
 
+/* Arguments of b200moe_dispatch_static(): the tensors of the dispatch stage as
+ * plain device pointers. Inputs: x [T,H] bf16, ids [T,K] int32/int64,
+ * routing_weights [T,K] float32. Outputs (caller-owned device memory):
+ * counts/offsets/cursors [E] int32, tasks [E+1] int32, ranks/mapping [T*K] int32,
+ * grouped_input [T*K,H] bf16, status [1] int32. */
+typedef struct {
+  int32_t tokens, experts, topk, hidden;
+  int32_t ids_are_int64;
+  int32_t token_tile; /* rows of one expert per tile, for the `tasks` prefix (> 0) */
+  const void* x;
+  const void* ids;
+  const void* routing_weights;
+  void* counts;
+  void* offsets;
+  void* cursors;
+  void* tasks;
+  void* ranks;
+  void* mapping;
+  void* grouped_input;
+  void* status;
+} B200MoeDispatchArgs;
+
+/* Most routes (T*K) b200moe_dispatch_static() accepts. */
+#define B200MOE_STATIC_DISPATCH_MAX_ROUTES 65536
+
+/* Ranked dispatch for callers that must not allocate device memory. This entry
+ * point has no counterpart in the reference project. It is for hosts that
+ * embed the library where cudaMalloc is off limits once the process is
+ * running: inside another framework's memory pool, in a real-time loop, or
+ * behind a plug-in interface that hands out only the input and output buffers.
+ * It gives the same counts / offsets / tasks / ranks / mapping / grouped_input /
+ * status as b200moe_dispatch(), but needs no plan and no workspace from the
+ * caller: the partition histograms of the counting kernels live in one
+ * fixed array inside the library (about 0.5 MiB of device memory on every GPU
+ * that loads the library, held until the process exits). Limits and rules:
+ *  - T*K <= B200MOE_STATIC_DISPATCH_MAX_ROUTES, E <= 256, K <= 32; larger sizes are
+ *    refused with B200MOE_ERR_INVALID, nothing is launched.
+ *  - The first call on each device looks up the device address of that array
+ *    (on the device that is current at the call); make that first call outside
+ *    any stream capture. Later calls only enqueue three kernels and one
+ *    4-byte memset on `cuda_stream`.
+ *  - All calls on a device share the array: two calls that can overlap on the
+ *    GPU (different streams, no dependency) race. Order them on one stream or
+ *    with events. Nothing needs to be cleared by the caller between calls.
+ *  - It calls no cudaMalloc / cudaFree or other allocating routine. */
+int b200moe_dispatch_static(const B200MoeDispatchArgs* args, void* cuda_stream);
+
 void b200moe_plan_destroy(B200MoePlan* plan);
 
 #ifdef __cplusplus

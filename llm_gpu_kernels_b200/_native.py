@@ -52,6 +52,17 @@ class Buffers(ctypes.Structure):
     _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS]
 
 
+class DispatchArgs(ctypes.Structure):
+    """Arguments of ``b200moe_dispatch_static`` (the entry point that allocates nothing)."""
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "tokens", "experts", "topk", "hidden", "ids_are_int64", "token_tile")] + [
+        (name, ctypes.c_void_p) for name in (
+            "x", "ids", "routing_weights", "counts", "offsets", "cursors", "tasks", "ranks", "mapping",
+            "grouped_input", "status")]
+
+
+STATIC_DISPATCH_MAX_ROUTES = 65536
+
 EXPORTS = {
     "b200moe_abi_version": (ctypes.c_int, []),
     "b200moe_last_error": (ctypes.c_char_p, []),
@@ -64,6 +75,7 @@ EXPORTS = {
     "b200moe_gate_up": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_down": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "b200moe_dispatch_static": (ctypes.c_int, [ctypes.POINTER(DispatchArgs), ctypes.c_void_p]),
     "b200moe_plan_destroy": (None, [ctypes.c_void_p]),
 }
 

@@ -331,3 +331,125 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
 }
 
 }  // namespace b200moe
+
+// ---------------------------------------------------------------------------------------------
+// b200moe_dispatch_static: the same ranked dispatch for callers that cannot allocate device
+// memory (a host that owns the GPU's memory pool, a real-time loop, a plug-in that is only
+// handed its input and output buffers). The partition histograms that b200moe_dispatch()
+// keeps in the caller's `scratch` workspace live here in one fixed device array, sized for
+// B200MOE_STATIC_DISPATCH_MAX_ROUTES routes and 256 experts: 512 partitions x 256 experts
+// + 64 block flags + 1 router-flag word, rounded up = 131328 int32 (513 KiB per GPU, held
+// from library load to process exit). The array is shared by every call on the device and
+// keeps what the last call left in it: the histogram and block-flag words are fully rewritten
+// by the counting kernel before anything reads them; the one word that must start at zero
+// (the router flag the scan kernel folds into `status`) is cleared on the stream by each call.
+// Calls that may overlap on the GPU race on the array. No allocation routine is called.
+#include <mutex>
+
+namespace b200moe {
+namespace {
+
+constexpr int kStaticScratchInts = 512 * 256 + 64 + 1 + 191;  // 131328
+static_assert(kStaticScratchInts % 64 == 0, "keep the array a whole number of 256-byte lines");
+static __device__ __align__(256) int g_static_dispatch_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+int* g_static_ptr[kMaxDevices] = {};  // device address of the array, per device, looked up once
+
+// In host code the array's name is only a handle for the runtime; the address a kernel can
+// use comes from cudaGetSymbolAddress on the device that is current.
+int static_scratch_for_current_device(int** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) {
+    set_error("cudaGetDevice: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  if (device < 0 || device >= kMaxDevices) {
+    set_error("device index %d outside the supported range", device);
+    return B200MOE_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[device]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_dispatch_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("cudaGetSymbolAddress(static dispatch scratch): %s", cudaGetErrorString(e));
+      return B200MOE_ERR_CUDA;
+    }
+    g_static_ptr[device] = static_cast<int*>(ptr);
+  }
+  *out = g_static_ptr[device];
+  return B200MOE_OK;
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_dispatch_static(const B200MoeDispatchArgs* a, void* cuda_stream) {
+  using namespace b200moe;
+  if (!a) {
+    set_error("null argument");
+    return B200MOE_ERR_INVALID;
+  }
+  if (a->tokens < 0 || a->experts < 1 || a->experts > 256 || a->topk < 1 || a->topk > 32 || a->hidden <= 0 ||
+      a->token_tile <= 0) {
+    set_error("static dispatch: needs T >= 0, E in [1,256], K in [1,32], H > 0, token_tile > 0");
+    return B200MOE_ERR_INVALID;
+  }
+  const long long routes = static_cast<long long>(a->tokens) * a->topk;
+  if (routes > B200MOE_STATIC_DISPATCH_MAX_ROUTES) {
+    set_error("static dispatch: %lld routes exceed the built-in scratch (at most %d routes); "
+              "use b200moe_dispatch with a caller-provided workspace", routes, B200MOE_STATIC_DISPATCH_MAX_ROUTES);
+    return B200MOE_ERR_INVALID;
+  }
+  if (routes == 0) return B200MOE_OK;
+  const void* needed[] = {a->x, a->ids, a->routing_weights, a->counts, a->offsets, a->cursors, a->tasks,
+                          a->ranks, a->mapping, a->grouped_input, a->status};
+  for (const void* ptr : needed)
+    if (!ptr) {
+      set_error("static dispatch: null buffer");
+      return B200MOE_ERR_INVALID;
+    }
+  int* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+
+  B200MoePlan p;  // host-side description only; nothing is allocated
+  p.shape.tokens = a->tokens;
+  p.shape.experts = a->experts;
+  p.shape.topk = a->topk;
+  p.shape.hidden = a->hidden;
+  p.shape.ids_are_int64 = a->ids_are_int64;
+  p.routes = static_cast<int>(routes);
+  p.token_tile = a->token_tile;
+  p.dispatch_fused = false;  // the multi-kernel path: the one that uses global scratch
+  const int per_warp = static_cast<int>(((routes + 511) / 512 + 31) / 32 * 32);
+  p.warp_routes = per_warp < 128 ? 128 : per_warp;
+  p.partitions = static_cast<int>((routes + p.warp_routes - 1) / p.warp_routes);
+  if (router_flag_index(p) + 1 > static_cast<size_t>(kStaticScratchInts)) {
+    set_error("static dispatch: internal scratch bound exceeded");
+    return B200MOE_ERR_INVALID;
+  }
+  p.buf.x = a->x;
+  p.buf.ids = const_cast<void*>(a->ids);
+  p.buf.routing_weights = const_cast<void*>(a->routing_weights);
+  p.buf.counts = a->counts;
+  p.buf.offsets = a->offsets;
+  p.buf.cursors = a->cursors;
+  p.buf.tasks = a->tasks;
+  p.buf.ranks = a->ranks;
+  p.buf.mapping = a->mapping;
+  p.buf.grouped_input = a->grouped_input;
+  p.buf.status = a->status;
+  p.buf.scratch = scratch;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemsetAsync(scratch + router_flag_index(p), 0, sizeof(int), stream);
+  if (e == cudaSuccess) e = launch_dispatch(p, stream);
+  if (e != cudaSuccess) {
+    set_error("static dispatch launch: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
