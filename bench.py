@@ -123,16 +123,21 @@ def event_ms(fn, steps, stream):
     return start.elapsed_time(end) / steps
 
 
-def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx):
-    """Prepare one layer at T tokens and time it: graph replay, eager, gate/up stage, end to end."""
+def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=None):
+    """Prepare one layer at T tokens and time it: graph replay, eager, gate/up stage, end to end.
+    `packed` = (PackedGateUp gate/up, PackedGateUp down) on the device selects the W4A16 path."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    from llm_gpu_kernels_b200.moe_w4_cuda import prepare_w4_moe
     from oracle.moe_oracle import algorithmic_work
     wr, gate_up, down, x_host = weights
     e, h, i, k = QWEN["experts"], QWEN["hidden"], QWEN["intermediate"], QWEN["topk"]
     x = x_host.to(dev)
     ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
     rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
-    prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr)
+    if packed is None:
+        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr)
+    else:
+        prepared = prepare_w4_moe(x, packed[0], None, ids, rw, packed_down=packed[1], router_weight=wr)
     base = prepared.base
     stream = torch.cuda.current_stream(dev)
     for _ in range(max(3, warmup)):
@@ -189,9 +194,11 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx):
     e2e_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
 
-    flops, nbytes = algorithmic_work(tokens, e, k, h, i, active)
+    w4 = packed is not None
+    flops, nbytes = algorithmic_work(tokens, e, k, h, i, active, w4=w4)
     t_roof_ms = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)) * 1e3
-    gate_up_bytes = active * 2 * i * h * 2 + tokens * k * h * 2 + tokens * k * i * 2
+    gate_up_weight_bytes = 2 * i * h * 2 if not w4 else 2 * i * h // 2 + 2 * i * (h // 128) * 2
+    gate_up_bytes = active * gate_up_weight_bytes + tokens * k * h * 2 + tokens * k * i * 2
     gate_up_gbs = gate_up_bytes / (stage_ms["gate_up_swiglu"] * 1e-3) / 1e9
     return {
         "tokens": tokens, "ms_graph": graph_ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms,
@@ -255,6 +262,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--tokens", type=int, default=1024, help="headline batch size")
+    ap.add_argument("--weights", default="bf16", choices=("bf16", "w4"),
+                    help="w4: gate/up and down packed W4G128 (int4 + BF16 group scales), BF16 activations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-headline", action="store_true", help="time only --tokens (short profiling runs)")
     args = ap.parse_args()
@@ -283,13 +292,23 @@ def main():
         xs = {t: v for t, v in xs.items() if t == args.tokens}
     if args.tokens not in xs:
         xs[args.tokens] = torch.randn(args.tokens, QWEN["hidden"], generator=g).bfloat16()
-    wr_d, gate_up_d, down_d = (t.to(dev) for t in weights_cpu)
+    packed = None
+    if args.weights == "w4":
+        from llm_gpu_kernels_b200.moe_weight_quant import (dequantize_gate_up_reference, quantize_down,
+                                                            quantize_gate_up)
+        pg, pd = quantize_gate_up(gate_up), quantize_down(down)
+        packed = (pg.to(dev), pd.to(dev))
+        # the CPU baseline evaluates the FP32 oracle on the dequantised weights
+        weights_cpu = (wr, dequantize_gate_up_reference(pg), dequantize_gate_up_reference(pd))
+        wr_d, gate_up_d, down_d = wr.to(dev), None, None
+    else:
+        wr_d, gate_up_d, down_d = (t.to(dev) for t in weights_cpu)
 
     results = {}
     with ClockSampler(local_rank) as clocks:
         for tokens in sorted(xs):
             results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
-                                           args.warmup, peaks, dist_ctx)
+                                           args.warmup, peaks, dist_ctx, packed=packed)
     head = results[args.tokens]
 
     # every rank runs the same full layer on its own batch (replicas); max over ranks
@@ -312,15 +331,17 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"Qwen3-30B-A3B MoE layer forward (router+dispatch+gate/up SwiGLU+down+combine), "
-                               f"T={args.tokens} tokens per GPU, E128 H2048 I768 top-8, BF16",
+                               f"T={args.tokens} tokens per GPU, E128 H2048 I768 top-8, "
+                               + ("BF16" if packed is None else "W4A16 (W4G128 gate/up and down, BF16 activations)"),
                    "timing": "CUDA-graph replay of one forward per step, CUDA events",
-                   "l2": "inputs larger than L2: 1.2 GB of expert weights streamed per step",
+                   "l2": "inputs larger than L2: %s of expert weights streamed per step" % (
+                       "1.2 GB" if packed is None else "0.31 GB"),
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                    "token_tile": head["token_tile"], "schedule": head["schedule"],
                    "active_experts": head["active_experts"]},
         "roofline": {"bound": "hbm", "achieved": head["gate_up_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": head["gate_up_gbs"] / peaks["hbm_gbs"], "traffic": None,
-                     "kernel": "grouped_gemm_tc_kernel<gate_up>", "peak_source": peaks["source"],
+                     "kernel": "grouped_gemm_tc_kernel<gate_up>" if packed is None else "grouped_gemm_w4_kernel<gate_up>", "peak_source": peaks["source"],
                      "alg_bytes_per_launch": head["gate_up_alg_bytes"],
                      "ms_per_launch": head["stage_ms"]["gate_up_swiglu"],
                      "layer": {"alg_bytes": head["alg_bytes"], "alg_flops": head["alg_flops"],

@@ -22,9 +22,12 @@ namespace {
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
+bool is_w4(int format) { return format == B200MOE_WEIGHTS_W4G128; }
+
 bool tc_shape_ok(const B200MoeShape& s) {
-  return s.hidden % 8 == 0 && s.intermediate % 8 == 0 && s.hidden >= 64 && s.intermediate >= 64 &&
-         s.gate_up_format == B200MOE_WEIGHTS_BF16 && s.down_format == B200MOE_WEIGHTS_BF16;
+  if (is_w4(s.gate_up_format) && s.hidden % 128) return false;    // one scale per 128 along K
+  if (is_w4(s.down_format) && s.intermediate % 128) return false;
+  return s.hidden % 8 == 0 && s.intermediate % 8 == 0 && s.hidden >= 64 && s.intermediate >= 64;
 }
 
 int auto_token_tile(long long routes, int experts) {
@@ -49,6 +52,28 @@ EncodeTiledFn encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   }
   return fn;
+}
+
+// Packed int4 weights as a 2-D int32 tensor [rows, words_per_row]; box = 8 words (64 nibbles) x 128 rows,
+// stored in shared memory exactly as in global memory (no swizzle).
+int encode_words(CUtensorMap* map, const void* base, uint64_t rows, uint64_t words_per_row) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return B200MOE_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {words_per_row, rows};
+  const cuuint64_t strides[1] = {words_per_row * 4};
+  const cuuint32_t box[2] = {8, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (packed words) failed with CUresult %d", static_cast<int>(r));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
 }
 
 // 2-D BF16 row-major [rows, cols] tensor, box = 64 columns x box_rows, 128-byte swizzle.
@@ -132,10 +157,16 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
     return B200MOE_ERR_UNSUPPORTED;
   }
   for (int f : {s.gate_up_format, s.down_format}) {
-    if (f != B200MOE_WEIGHTS_BF16) {
-      set_error("weight format %d is not available in this build", f);
-      return B200MOE_ERR_UNSUPPORTED;
+    if (f != B200MOE_WEIGHTS_BF16 && f != B200MOE_WEIGHTS_W4G128) {
+      set_error("unknown weight format %d", f);
+      return B200MOE_ERR_INVALID;
     }
+  }
+  const bool any_w4 = is_w4(s.gate_up_format) || is_w4(s.down_format);
+  if (any_w4 && (s.schedule == B200MOE_SCHEDULE_GENERIC || !tc_shape_ok(s))) {
+    set_error("W4G128 weights need the tcgen05 schedule: K a multiple of 128 (H=%d for gate/up, I=%d for down), "
+              "H and I multiples of 8", s.hidden, s.intermediate);
+    return B200MOE_ERR_UNSUPPORTED;
   }
   int schedule = s.schedule;
   if (schedule == B200MOE_SCHEDULE_AUTO) schedule = tc_shape_ok(s) ? B200MOE_SCHEDULE_TCGEN05 : B200MOE_SCHEDULE_GENERIC;
@@ -144,7 +175,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
     return B200MOE_ERR_INVALID;
   }
   if (schedule == B200MOE_SCHEDULE_TCGEN05 && !tc_shape_ok(s)) {
-    set_error("tcgen05 schedule needs BF16 weights, H and I multiples of 8 and >= 64 (H=%d I=%d)", s.hidden,
+    set_error("tcgen05 schedule needs H and I multiples of 8 and >= 64 (H=%d I=%d)", s.hidden,
               s.intermediate);
     return B200MOE_ERR_UNSUPPORTED;
   }
@@ -286,11 +317,28 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
         return B200MOE_ERR_INVALID;
       }
     const uint64_t E = s.experts, H = s.hidden, I = s.intermediate, R = p->routes;
-    if ((rc = encode_2d(&p->tm_gate_up_w, b->gate_up, E * 2 * I, H, 128, true))) return rc;
+    if (is_w4(s.gate_up_format)) {
+      if (!b->gate_up_scales) {
+        set_error("W4G128 gate/up needs gate_up_scales");
+        return B200MOE_ERR_INVALID;
+      }
+      if ((rc = encode_words(&p->tm_gate_up_w, b->gate_up, E * 2 * I, H / 8))) return rc;
+    } else if ((rc = encode_2d(&p->tm_gate_up_w, b->gate_up, E * 2 * I, H, 128, true))) {
+      return rc;
+    }
+    if (is_w4(s.down_format)) {
+      if (!b->down_scales) {
+        set_error("W4G128 down needs down_scales");
+        return B200MOE_ERR_INVALID;
+      }
+      if ((rc = encode_words(&p->tm_down_w, b->down, E * H, I / 8))) return rc;
+    } else if ((rc = encode_2d(&p->tm_down_w, b->down, E * H, I, 128, true))) {
+      return rc;
+    }
     if ((rc = encode_2d(&p->tm_grouped, b->grouped_input, R, H, p->token_tile, false))) return rc;
-    if ((rc = encode_2d(&p->tm_down_w, b->down, E * H, I, 128, true))) return rc;
     if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->token_tile, false))) return rc;
     if ((rc = configure_tc(*p))) return rc;
+    if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && (rc = configure_w4(*p))) return rc;
   }
   p->bound = true;
   return B200MOE_OK;
@@ -316,7 +364,8 @@ int b200moe_gate_up(B200MoePlan* p, void* stream) {
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return check_cuda(p->schedule == B200MOE_SCHEDULE_TCGEN05 ? launch_gate_up_tc(*p, s) : launch_gate_up_generic(*p, s),
+  if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_gate_up_generic(*p, s), "gate_up launch");
+  return check_cuda(is_w4(p->shape.gate_up_format) ? launch_gate_up_w4(*p, s) : launch_gate_up_tc(*p, s),
                     "gate_up launch");
 }
 
@@ -325,8 +374,8 @@ int b200moe_down(B200MoePlan* p, void* stream) {
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return check_cuda(p->schedule == B200MOE_SCHEDULE_TCGEN05 ? launch_down_tc(*p, s) : launch_down_generic(*p, s),
-                    "down launch");
+  if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
+  return check_cuda(is_w4(p->shape.down_format) ? launch_down_w4(*p, s) : launch_down_tc(*p, s), "down launch");
 }
 
 int b200moe_combine(B200MoePlan* p, void* stream) {

@@ -30,21 +30,18 @@
 #include <cuda.h>
 #include "plan.h"
 #include "sm100_ptx.cuh"
+#include "gemm_tile.cuh"
 
 namespace b200moe {
 namespace {
 
 using namespace ptx;
+using namespace tile;
 
-constexpr int kBlockK = 64;                    // bf16 per k-block: 128 bytes = one swizzle row
-constexpr int kTileM = 128;                    // output channels per tile (UMMA M)
-constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 12;
-constexpr int kMaxExperts = 256;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
-constexpr int kSmemLimit = 232448;             // 227 KB opt-in limit per CTA
 
 struct Ctrl {
   uint64_t full[kMaxStages];
@@ -54,36 +51,9 @@ struct Ctrl {
   uint64_t drain;
   uint32_t tmem_base;
   int abort;
-  int tasks[kMaxExperts + 1];
-  int offsets[kMaxExperts];
-  int counts[kMaxExperts];
+  Tables tables;
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
-
-struct Tile {
-  int expert, ct, row0, rows, n_eff;
-};
-
-// item -> (expert, channel tile, token tile). Items of one expert are ordered
-// channel tile major, token tile fastest, so CTAs running side by side share a
-// weight tile (L2) when an expert has several token tiles.
-__device__ __forceinline__ Tile decode_tile(const Ctrl* c, int item, int E, int n_ct, int token_tile) {
-  int lo = 0, hi = E;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (item >= c->tasks[mid + 1] * n_ct) lo = mid + 1; else hi = mid;
-  }
-  Tile t;
-  t.expert = lo;
-  const int local = item - c->tasks[lo] * n_ct;
-  const int tiles = c->tasks[lo + 1] - c->tasks[lo];
-  t.ct = local / tiles;
-  const int tt = local - t.ct * tiles;
-  t.row0 = c->offsets[lo] + tt * token_tile;
-  t.rows = min(token_tile, c->counts[lo] - tt * token_tile);
-  t.n_eff = max(16, (t.rows + 15) & ~15);
-  return t;
-}
 
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -106,11 +76,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i <= E; i += kThreads) c->tasks[i] = g_tasks[i];
-  for (int i = threadIdx.x; i < E; i += kThreads) {
-    c->offsets[i] = g_offsets[i];
-    c->counts[i] = g_counts[i];
-  }
+  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(&c->full[s], 1);
@@ -134,7 +100,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 
   const int n_ct = (n_out + kTileM - 1) / kTileM;
   const int num_kb = (k_dim + kBlockK - 1) / kBlockK;
-  const int total_items = c->tasks[E] * n_ct;
+  const int total_items = c->tables.tasks[E] * n_ct;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -146,7 +112,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       long long issued = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) { ok = false; break; }
@@ -175,7 +141,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
         if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
         tc_fence_after();
@@ -211,27 +177,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const Tile t = decode_tile(c, item, E, n_ct, token_tile);
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
       // warp-uniform outcome: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
-      const int channel = t.ct * kTileM + quarter * 32 + lane;
-      const bool ch_ok = channel < n_out;
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16* dst = out + static_cast<size_t>(t.row0) * n_out + channel;
-      for (int n0 = 0; n0 < t.n_eff; n0 += 16) {
-        uint32_t g[16], u[16];
-        tmem_ld16(taddr + n0, g);
-        if (kGateUp) tmem_ld16(taddr + token_tile + n0, u);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int n = n0 + j;
-          float v = __uint_as_float(g[j]);
-          if (kGateUp) v = (v / (1.0f + __expf(-v))) * __uint_as_float(u[j]);
-          if (ch_ok && n < t.rows) dst[static_cast<size_t>(n) * n_out] = __float2bfloat16_rn(v);
-        }
-      }
+      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
       mbar_arrive(&c->tmem_empty[acc]);
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }

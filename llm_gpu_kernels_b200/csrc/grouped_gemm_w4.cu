@@ -1,0 +1,328 @@
+// W4A16 ragged grouped GEMM: packed int4 weights (the reference's W4G128 v1
+// format) are TMA-loaded to shared memory as stored, dequantised to BF16 by
+// converter warps straight into the 128-byte-swizzled operand tile, and
+// multiplied on tcgen05 with the accumulators in tensor memory.
+//
+// Format contract (reference moe_weight_quant.py:1-6,35-52 and the device decode
+// of cuda_w4_gate_up.cu:28-41): words[e][n][kw] holds K = 8*kw .. 8*kw+7, nibble j
+// at bits [4j,4j+4), nibble = q + 8 with q in [-7,7]; one BF16 scale per
+// (expert, output channel, 128 consecutive K); the operand fed to the MMA is
+// exactly bf16_rn(float(q) * float(scale)). Here: (w >> 4j) & 0x000F000F | 0x43004300
+// gives the BF16 pair {128 + n_j, 128 + n_(j+4)}, minus 136 is the exact integer
+// q, and one BF16 multiply by the scale rounds once - the same value.
+// The reference quantises gate/up only; the same format with K = I serves down.
+//
+// Schedule: as grouped_gemm_tcgen05.cu (swap-AB, per-tile N, persistent,
+// device-side tile list) plus eight converter warps and two rings: packed
+// stages (words + activation rows, filled by TMA) and operand stages (BF16
+// weight tiles, filled by the converters).
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include "plan.h"
+#include "sm100_ptx.cuh"
+#include "gemm_tile.cuh"
+
+namespace b200moe {
+namespace {
+
+using namespace ptx;
+using namespace tile;
+
+constexpr int kConverters = 256;                       // 8 warps
+constexpr int kThreads = 192 + kConverters;            // TMA, MMA, 4 epilogue, 8 converter warps
+constexpr int kMaxPacked = 12, kMaxOperand = 4;
+constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile: 16 KB
+constexpr uint32_t kPackedTileBytes = kTileM * kBlockK / 2;  // the same tile packed: 4 KB
+constexpr int kCtrlBytes = 4096;
+
+struct Ctrl {
+  uint64_t packed_full[kMaxPacked];
+  uint64_t packed_empty[kMaxPacked];
+  uint64_t op_full[kMaxOperand];
+  uint64_t op_empty[kMaxOperand];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+  Tables tables;
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+// Eight nibbles of one word -> eight BF16 in K order, scaled: one 16-byte chunk of the operand row.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 scale2) {
+  const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
+  uint32_t pair[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + n_j, 128 + n_(j+4)}
+    __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
+    q = __hmul2(q, scale2);
+    pair[j] = *reinterpret_cast<uint32_t*>(&q);
+  }
+  uint4 out;
+  out.x = __byte_perm(pair[0], pair[1], 0x5410);  // k0 k1
+  out.y = __byte_perm(pair[2], pair[3], 0x5410);  // k2 k3
+  out.z = __byte_perm(pair[0], pair[1], 0x7632);  // k4 k5
+  out.w = __byte_perm(pair[2], pair[3], 0x7632);  // k6 k7
+  return out;
+}
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __grid_constant__ CUtensorMap tm_act,
+                       const __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
+                       const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
+                       int w_rows_per_expert, int token_tile, int num_packed, int num_operand, int stream_weights) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t ring_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
+  constexpr uint32_t kOpBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;        // operand stage
+  constexpr uint32_t kWordsBytes = kGateUp ? 2 * kPackedTileBytes : kPackedTileBytes;
+  const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
+  const uint32_t packed_bytes = kWordsBytes + act_bytes;                        // packed stage
+  unsigned char* op_ring = smem_raw + ring_off;
+  unsigned char* packed_ring = op_ring + static_cast<size_t>(num_operand) * kOpBytes;
+  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < num_packed; ++s) {
+      mbar_init(&c->packed_full[s], 1);
+      mbar_init(&c->packed_empty[s], kConverters + 1);  // every converter thread + the MMA commit
+    }
+    for (int s = 0; s < num_operand; ++s) {
+      mbar_init(&c->op_full[s], kConverters);
+      mbar_init(&c->op_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_empty[a], 128);
+    }
+    mbar_init(&c->drain, 1);
+    c->abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
+
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const int num_kb = k_dim / kBlockK;  // K is a multiple of 128
+  const int groups = k_dim / 128;
+  const int total_items = c->tables.tasks[E] * n_ct;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      const uint64_t pol_w = stream_weights ? policy_evict_first() : policy_evict_last();
+      const uint64_t pol_act = policy_evict_last();
+      int p = 0;
+      uint32_t pph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->packed_empty[p], pph ^ 1u, &c->abort, status)) { ok = false; break; }
+          unsigned char* st = packed_ring + static_cast<size_t>(p) * packed_bytes;
+          mbar_expect_tx(&c->packed_full[p], packed_bytes);
+          tma_load_2d(st, &tm_words, &c->packed_full[p], kb * 8, w_row, pol_w);  // 8 int32 = 64 nibbles
+          if (kGateUp) tma_load_2d(st + kPackedTileBytes, &tm_words, &c->packed_full[p], kb * 8, w_row + n_out, pol_w);
+          tma_load_2d(st + kWordsBytes, &tm_act, &c->packed_full[p], kb * kBlockK, t.row0, pol_act);
+          ++issued;
+          if (++p == num_packed) { p = 0; pph ^= 1u; }
+        }
+      }
+      const long long first = issued > num_packed ? issued - num_packed : 0;
+      for (long long i = first; i < issued; ++i) {  // never leave with copies in flight
+        if (!mbar_wait_plain(&c->packed_full[i % num_packed], static_cast<uint32_t>((i / num_packed) & 1))) {
+          atomicOr(status, B200MOE_STATUS_TIMEOUT);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      int p = 0, q = 0, acc = 0;
+      uint32_t pph = 0, qph = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
+        if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
+        const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->packed_full[p], pph, &c->abort, status) ||
+              !mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(op_ring + static_cast<size_t>(q) * kOpBytes);
+          const uint32_t a_addr = smem_u32(packed_ring + static_cast<size_t>(p) * packed_bytes + kWordsBytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
+            const uint64_t bdesc = umma_desc(a_addr + k * kUmmaK * 2);
+            umma(d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+            if (kGateUp) umma(d_up, umma_desc(w_addr + kWTileBytes + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+          }
+          umma_commit(&c->op_empty[q]);
+          umma_commit(&c->packed_empty[p]);
+          if (++p == num_packed) { p = 0; pph ^= 1u; }
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&c->tmem_full[acc]);
+        if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) {
+        umma_commit(&c->drain);
+        mbar_wait_plain(&c->drain, 0);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
+      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      tc_fence_before();
+      mbar_arrive(&c->tmem_empty[acc]);
+      if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ converter warps
+    const int tid = threadIdx.x - 192;
+    const int row = tid & 127, half = tid >> 7;
+    // gate/up: half 0 converts the gate tile, half 1 the up tile, a whole row each (8 words);
+    // down: both halves share the one tile, four words each.
+    const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
+    int p = 0, q = 0;
+    uint32_t pph = 0, qph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+      long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row +
+                       (kGateUp ? half * n_out : 0);
+      if (srow >= total_rows) srow = total_rows - 1;  // lanes past the last channel are never stored
+      const __nv_bfloat16* srow_ptr = scales + srow * groups;
+      __nv_bfloat16 s_next = srow_ptr[0];
+      __nv_bfloat162 scale2 = __bfloat162bfloat162(s_next);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if ((kb & 1) == 0) {
+          scale2 = __bfloat162bfloat162(s_next);
+          if (kb / 2 + 1 < groups) s_next = srow_ptr[kb / 2 + 1];  // next group's scale, used two k-blocks later
+        }
+        if (!mbar_wait(&c->packed_full[p], pph, &c->abort, status) ||
+            !mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
+        const unsigned char* words = packed_ring + static_cast<size_t>(p) * packed_bytes;
+        unsigned char* dst = op_ring + static_cast<size_t>(q) * kOpBytes + row * 128;
+        if (kGateUp) {
+          const uint4* src = reinterpret_cast<const uint4*>(words + half * kPackedTileBytes + row * 32);
+          dst += half * kWTileBytes;
+          const uint4 w0 = src[0], w1 = src[1];
+          const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = dequant_word(w[j], scale2);
+        } else {
+          const uint4 w0 = *reinterpret_cast<const uint4*>(words + row * 32 + half * 16);
+          const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(dst + (((half * 4 + j) ^ (row & 7)) << 4)) = dequant_word(w[j], scale2);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+        mbar_arrive(&c->op_full[q]);
+        mbar_arrive(&c->packed_empty[p]);
+        if (++p == num_packed) { p = 0; pph ^= 1u; }
+        if (++q == num_operand) { q = 0; qph ^= 1u; }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+void rings_for(bool gate_up, int token_tile, int* num_packed, int* num_operand, int* smem_bytes) {
+  const int op = (gate_up ? 2 : 1) * static_cast<int>(kWTileBytes);
+  const int packed = (gate_up ? 2 : 1) * static_cast<int>(kPackedTileBytes) + token_tile * 128;
+  const int budget = kSmemLimit - kCtrlBytes - 1024;
+  int q = gate_up ? 3 : 4;
+  int p = (budget - q * op) / packed;
+  while (p < 3 && q > 2) {
+    --q;
+    p = (budget - q * op) / packed;
+  }
+  if (p > kMaxPacked) p = kMaxPacked;
+  *num_packed = p;
+  *num_operand = q;
+  *smem_bytes = kCtrlBytes + 1024 + q * op + p * packed;
+}
+
+template <bool kGateUp>
+cudaError_t launch_w4(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  const int n_out = kGateUp ? sh.intermediate : sh.hidden;
+  const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
+  const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
+  const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
+  grouped_gemm_w4_kernel<kGateUp><<<grid, kThreads, kGateUp ? p.w4_smem_gate_up : p.w4_smem_down, s>>>(
+      kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
+      static_cast<const __nv_bfloat16*>(kGateUp ? p.buf.gate_up_scales : p.buf.down_scales),
+      static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
+      static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
+      static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
+      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, kGateUp ? p.w4_packed_gate_up : p.w4_packed_down,
+      kGateUp ? p.w4_operand_gate_up : p.w4_operand_down, stream_weights);
+  return cudaPeekAtLastError();
+}
+
+}  // namespace
+
+int configure_w4(B200MoePlan& p) {
+  rings_for(true, p.token_tile, &p.w4_packed_gate_up, &p.w4_operand_gate_up, &p.w4_smem_gate_up);
+  rings_for(false, p.token_tile, &p.w4_packed_down, &p.w4_operand_down, &p.w4_smem_down);
+  if (p.w4_packed_gate_up < 2 || p.w4_packed_down < 2) {
+    set_error("token_tile %d leaves fewer than 2 packed stages", p.token_tile);
+    return B200MOE_ERR_INVALID;
+  }
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_w4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_gemm_w4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(W4 shared memory) failed: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s) { return launch_w4<true>(p, s); }
+cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s) { return launch_w4<false>(p, s); }
+
+}  // namespace b200moe

@@ -20,9 +20,9 @@ struct B200MoePlan {
   int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
   bool dispatch_fused = false;  // one-block count + scan + mapping (R <= kFusedRoutes)
   // TMA descriptors (tcgen05 schedule)
-  CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128
+  CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128  (W4: [E*2I, H/8] int32, box 8 x 128)
   CUtensorMap tm_grouped{};     // [R, H] bf16, box 64 x token_tile
-  CUtensorMap tm_down_w{};      // [E*H, I] bf16, box 64 x 128
+  CUtensorMap tm_down_w{};      // [E*H, I] bf16, box 64 x 128   (W4: [E*H, I/8] int32, box 8 x 128)
   CUtensorMap tm_activated{};   // [R, I] bf16, box 64 x token_tile
   // router on the tensor cores (tcgen05 schedule with a router)
   bool router_tc = false;
@@ -31,6 +31,9 @@ struct B200MoePlan {
   int router_smem = 0, router_stages = 0;
   int gemm_smem_gate_up = 0, gemm_stages_gate_up = 0;
   int gemm_smem_down = 0, gemm_stages_down = 0;
+  // W4A16 kernels: packed-stage ring, operand-stage ring, dynamic shared memory
+  int w4_packed_gate_up = 0, w4_operand_gate_up = 0, w4_smem_gate_up = 0;
+  int w4_packed_down = 0, w4_operand_down = 0, w4_smem_down = 0;
 };
 
 namespace b200moe {
@@ -45,6 +48,8 @@ cudaError_t launch_gate_up_generic(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_generic(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
 
 size_t router_smem_bytes(int hidden, int experts);
@@ -53,6 +58,7 @@ cudaError_t router_opt_in_smem(size_t bytes);
 // One-time per-plan set-up of the tcgen05 kernels (smem opt-in, stage counts).
 int configure_tc(B200MoePlan& p);
 int configure_router_tc(B200MoePlan& p);
+int configure_w4(B200MoePlan& p);
 
 // The router raises its timeout flag in a scratch word (the dispatch folds it into the
 // status word, which it resets every forward): int32 index of that word inside `scratch`.

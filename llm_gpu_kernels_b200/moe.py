@@ -80,6 +80,9 @@ class PreparedMoE:
     ranks: torch.Tensor = None
     scratch: torch.Tensor = None
     router_weight: torch.Tensor = None
+    gate_up_scales: torch.Tensor = None  # set when gate_up holds packed W4G128 words
+    down_scales: torch.Tensor = None     # set when down holds packed W4G128 words
+    packed: object = None                # the PackedGateUp the plan was prepared from (reference W4Workspace.packed)
     schedule: str = ""
     token_tile: int = 0
     launches: tuple = ()
@@ -144,19 +147,41 @@ class PreparedMoE:
                 pass
 
 
-def _validate(x, gate_up, down, ids, routing_weights, router_weight):
-    for tensor, rank in ((x, 2), (gate_up, 3), (down, 3)):
-        _input(tensor, rank)
-    e, h, intermediate = down.shape
+def _packed_input(words, scales, name):
+    """Packed W4G128 operand: int32 words [E,N,K/8] and BF16 scales [E,N,K/128] (reference moe_w4_cuda.py:101-114)."""
+    if (not isinstance(words, torch.Tensor) or not isinstance(scales, torch.Tensor) or words.ndim != 3
+            or scales.ndim != 3 or words.dtype != torch.int32 or scales.dtype != torch.bfloat16
+            or not words.is_cuda or not scales.is_cuda or not words.is_contiguous() or not scales.is_contiguous()
+            or words.shape[:2] != scales.shape[:2] or words.shape[2] * 8 != scales.shape[2] * 128):
+        raise ValueError(f"{name}: packed shape/dtype mismatch (int32 words [E,N,K/8], BF16 scales [E,N,K/128])")
+    if words.data_ptr() % 16:
+        raise ValueError("16-byte input alignment required")
+
+
+def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales=None, down_scales=None):
+    _input(x, 2)
+    if gate_up_scales is None:
+        _input(gate_up, 3)
+        gate_up_shape = tuple(gate_up.shape)
+    else:
+        _packed_input(gate_up, gate_up_scales, "gate_up")
+        gate_up_shape = (gate_up.shape[0], gate_up.shape[1], gate_up.shape[2] * 8)
+    if down_scales is None:
+        _input(down, 3)
+        e, h, intermediate = down.shape
+    else:
+        _packed_input(down, down_scales, "down")
+        e, h, intermediate = down.shape[0], down.shape[1], down.shape[2] * 8
     if (not 0 < e <= 256 or h <= 0 or intermediate <= 0 or x.shape[1] != h
-            or tuple(gate_up.shape) != (e, 2 * intermediate, h)):
+            or gate_up_shape != (e, 2 * intermediate, h)):
         raise ValueError("invalid MoE shape; prototype requires E in [1,256], H/I positive")
     if (not isinstance(ids, torch.Tensor) or not isinstance(routing_weights, torch.Tensor) or ids.ndim != 2
             or ids.dtype not in (torch.int32, torch.int64) or ids.shape[0] != x.shape[0]
             or not 0 < ids.shape[1] <= 32 or routing_weights.shape != ids.shape
             or routing_weights.dtype != torch.float32):
         raise ValueError("expected CUDA IDs[T,topk<=32] and FP32 weights of identical shape")
-    if any(t.device != x.device or not t.is_contiguous() for t in (gate_up, down, ids, routing_weights)):
+    extra = [t for t in (gate_up_scales, down_scales) if t is not None]
+    if any(t.device != x.device or not t.is_contiguous() for t in (gate_up, down, ids, routing_weights, *extra)):
         raise ValueError("all MoE tensors must be contiguous and on the same CUDA device")
     r = ids.numel()
     if r >= 2**31 or r * max(h, 2 * intermediate) >= 2**31:
@@ -167,21 +192,27 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight):
             raise ValueError("router_weight must be [E,H] BF16 on the same device")
         if ids.shape[1] > e:
             raise ValueError("router needs topk <= experts")
+    return e, h, intermediate
 
 
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
-             token_tile=0, config=None, warm=True):
-    """Validate, allocate the workspace, bind the native plan, run one forward."""
-    _validate(x, gate_up, down, ids, routing_weights, router_weight)
+             token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None):
+    """Validate, allocate the workspace, bind the native plan, run one forward.
+
+    With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
+    W4G128 int32 word tensor instead of a BF16 tensor.
+    """
+    e, h, intermediate = _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales,
+                                   down_scales)
     if schedule not in _SCHEDULES:
         raise ValueError(f"unknown schedule {schedule!r}; expected one of auto/generic/tcgen05")
     lib = _native.load()
-    tokens, h = x.shape
-    e, _, intermediate = down.shape
+    tokens = x.shape[0]
     topk = ids.shape[1]
     shape = _native.Shape(tokens=tokens, experts=e, topk=topk, hidden=h, intermediate=intermediate,
                           ids_are_int64=int(ids.dtype == torch.int64),
-                          gate_up_format=_native.WEIGHTS_BF16, down_format=_native.WEIGHTS_BF16,
+                          gate_up_format=_native.WEIGHTS_BF16 if gate_up_scales is None else _native.WEIGHTS_W4G128,
+                          down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
                           use_router=int(router_weight is not None))
     handle = ctypes.c_void_p()
@@ -201,7 +232,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
             int32((1,)), config,
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
-            kernel_launches=sizes.launches)
+            kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales)
         expected = {"output": plan.output, "counts": plan.counts, "offsets": plan.offsets,
                     "cursors": plan.cursors, "tasks": plan.tasks, "mapping": plan.mapping, "ranks": plan.ranks,
                     "grouped_input": plan.grouped_input, "activated": plan.activated,
@@ -211,8 +242,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                 raise RuntimeError(f"workspace buffer {name} smaller than the library requires")
         ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
         buffers = _native.Buffers(
-            x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=None,
-            down=ptr(down), down_scales=None, ids=ptr(ids), routing_weights=ptr(routing_weights),
+            x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales),
+            down=ptr(down), down_scales=ptr(down_scales), ids=ptr(ids), routing_weights=ptr(routing_weights),
             **{name: ptr(tensor) for name, tensor in expected.items()})
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
