@@ -54,8 +54,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Packed int4 weights as a 2-D int32 tensor [rows, words_per_row]; box = 8 words (64 nibbles) x 128 rows,
-// stored in shared memory exactly as in global memory (no swizzle).
+// Packed int4 weights as a 2-D int32 tensor [rows, words_per_row]; box = 32 words (256 nibbles, 128 bytes)
+// x 128 rows, 128-byte swizzle (whole 128-byte rows keep HBM reads efficient; the swizzle keeps the
+// converters' shared-memory reads conflict-free).
 int encode_words(CUtensorMap* map, const void* base, uint64_t rows, uint64_t words_per_row) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
@@ -64,10 +65,10 @@ int encode_words(CUtensorMap* map, const void* base, uint64_t rows, uint64_t wor
   }
   const cuuint64_t dims[2] = {words_per_row, rows};
   const cuuint64_t strides[1] = {words_per_row * 4};
-  const cuuint32_t box[2] = {8, 128};
+  const cuuint32_t box[2] = {32, 128};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled (packed words) failed with CUresult %d", static_cast<int>(r));

@@ -84,7 +84,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&c->tmem_full[a], 1);
-      mbar_init(&c->tmem_empty[a], 128);
+      mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
     mbar_init(&c->drain, 1);
     c->abort = 0;
@@ -184,7 +184,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
-      mbar_arrive(&c->tmem_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   }

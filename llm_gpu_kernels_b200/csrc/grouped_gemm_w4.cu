@@ -13,9 +13,13 @@
 // The reference quantises gate/up only; the same format with K = I serves down.
 //
 // Schedule: as grouped_gemm_tcgen05.cu (swap-AB, per-tile N, persistent,
-// device-side tile list) plus eight converter warps and two rings: packed
-// stages (words + activation rows, filled by TMA) and operand stages (BF16
-// weight tiles, filled by the converters).
+// device-side tile list) plus eight converter warps, a second TMA warp and two rings:
+//  * words ring  - packed tiles of 128 channels x 256 K (one 128-byte row of words per
+//    channel, 128B-swizzled by TMA so the converters' 16-byte reads are conflict-free).
+//    Whole 128-byte rows matter: 32-byte rows (64 K per box) fetch HBM in 32-byte sectors
+//    and ran at a quarter of the bandwidth.
+//  * operand ring - per 64 K: the BF16 weight tile(s) written by the converters plus the
+//    activation rows written by the second TMA warp; consumed by the MMA warp.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
@@ -28,16 +32,17 @@ namespace {
 using namespace ptx;
 using namespace tile;
 
-constexpr int kConverters = 256;                       // 8 warps
-constexpr int kThreads = 192 + kConverters;            // TMA, MMA, 4 epilogue, 8 converter warps
-constexpr int kMaxPacked = 12, kMaxOperand = 4;
-constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile: 16 KB
-constexpr uint32_t kPackedTileBytes = kTileM * kBlockK / 2;  // the same tile packed: 4 KB
+constexpr int kConverters = 256;                       // 8 warps (warps 6..13)
+constexpr int kThreads = 192 + kConverters + 32;       // + words TMA, MMA, 4 epilogue, activation TMA warp
+constexpr int kMaxWords = 6, kMaxOperand = 4;
+constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
+constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
+constexpr uint32_t kWordsTileBytes = kTileM * kWordsK / 2;  // one packed tile of 256 K: 16 KB
 constexpr int kCtrlBytes = 4096;
 
 struct Ctrl {
-  uint64_t packed_full[kMaxPacked];
-  uint64_t packed_empty[kMaxPacked];
+  uint64_t words_full[kMaxWords];
+  uint64_t words_empty[kMaxWords];
   uint64_t op_full[kMaxOperand];
   uint64_t op_empty[kMaxOperand];
   uint64_t tmem_full[2];
@@ -74,17 +79,17 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
                        const __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
                        const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
-                       int w_rows_per_expert, int token_tile, int num_packed, int num_operand, int stream_weights) {
+                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
-  constexpr uint32_t kOpBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;        // operand stage
-  constexpr uint32_t kWordsBytes = kGateUp ? 2 * kPackedTileBytes : kPackedTileBytes;
+  constexpr uint32_t kOpWeightBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;
+  constexpr uint32_t kWordsBytes = kGateUp ? 2 * kWordsTileBytes : kWordsTileBytes;  // words stage
   const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
-  const uint32_t packed_bytes = kWordsBytes + act_bytes;                        // packed stage
+  const uint32_t op_bytes = kOpWeightBytes + act_bytes;                               // operand stage
   unsigned char* op_ring = smem_raw + ring_off;
-  unsigned char* packed_ring = op_ring + static_cast<size_t>(num_operand) * kOpBytes;
+  unsigned char* words_ring = op_ring + static_cast<size_t>(num_operand) * op_bytes;
   const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
@@ -93,17 +98,17 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < num_packed; ++s) {
-      mbar_init(&c->packed_full[s], 1);
-      mbar_init(&c->packed_empty[s], kConverters + 1);  // every converter thread + the MMA commit
+    for (int s = 0; s < num_words; ++s) {
+      mbar_init(&c->words_full[s], 1);
+      mbar_init(&c->words_empty[s], kConverters / 32);   // one arrival per converter warp
     }
     for (int s = 0; s < num_operand; ++s) {
-      mbar_init(&c->op_full[s], kConverters);
-      mbar_init(&c->op_empty[s], 1);
+      mbar_init(&c->op_full[s], kConverters / 32 + 1);   // converter warps + the activation TMA
+      mbar_init(&c->op_empty[s], 1);                     // the MMA commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&c->tmem_full[a], 1);
-      mbar_init(&c->tmem_empty[a], 128);
+      mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
     mbar_init(&c->drain, 1);
     c->abort = 0;
@@ -116,15 +121,15 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
 
   const int n_ct = (n_out + kTileM - 1) / kTileM;
-  const int num_kb = k_dim / kBlockK;  // K is a multiple of 128
+  const int num_kb = k_dim / kBlockK;                       // K is a multiple of 128
+  const int num_ws = (k_dim + kWordsK - 1) / kWordsK;       // words stages per tile
   const int groups = k_dim / 128;
   const int total_items = c->tables.tasks[E] * n_ct;
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---------------------------------------------------------------- TMA producer
+      // ---------------------------------------------------------------- TMA producer: packed words
       const uint64_t pol_w = stream_weights ? policy_evict_first() : policy_evict_last();
-      const uint64_t pol_act = policy_evict_last();
       int p = 0;
       uint32_t pph = 0;
       long long issued = 0;
@@ -132,30 +137,54 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&c->packed_empty[p], pph ^ 1u, &c->abort, status)) { ok = false; break; }
-          unsigned char* st = packed_ring + static_cast<size_t>(p) * packed_bytes;
-          mbar_expect_tx(&c->packed_full[p], packed_bytes);
-          tma_load_2d(st, &tm_words, &c->packed_full[p], kb * 8, w_row, pol_w);  // 8 int32 = 64 nibbles
-          if (kGateUp) tma_load_2d(st + kPackedTileBytes, &tm_words, &c->packed_full[p], kb * 8, w_row + n_out, pol_w);
-          tma_load_2d(st + kWordsBytes, &tm_act, &c->packed_full[p], kb * kBlockK, t.row0, pol_act);
+        for (int ws = 0; ws < num_ws; ++ws) {
+          if (!mbar_wait(&c->words_empty[p], pph ^ 1u, &c->abort, status)) { ok = false; break; }
+          unsigned char* st = words_ring + static_cast<size_t>(p) * kWordsBytes;
+          mbar_expect_tx(&c->words_full[p], kWordsBytes);
+          tma_load_2d(st, &tm_words, &c->words_full[p], ws * (kWordsK / 8), w_row, pol_w);  // 32 int32 per row
+          if (kGateUp)
+            tma_load_2d(st + kWordsTileBytes, &tm_words, &c->words_full[p], ws * (kWordsK / 8), w_row + n_out, pol_w);
           ++issued;
-          if (++p == num_packed) { p = 0; pph ^= 1u; }
+          if (++p == num_words) { p = 0; pph ^= 1u; }
         }
       }
-      const long long first = issued > num_packed ? issued - num_packed : 0;
+      const long long first = issued > num_words ? issued - num_words : 0;
       for (long long i = first; i < issued; ++i) {  // never leave with copies in flight
-        if (!mbar_wait_plain(&c->packed_full[i % num_packed], static_cast<uint32_t>((i / num_packed) & 1))) {
+        if (!mbar_wait_plain(&c->words_full[i % num_words], static_cast<uint32_t>((i / num_words) & 1))) {
           atomicOr(status, B200MOE_STATUS_TIMEOUT);
           break;
         }
       }
     }
+  } else if (warp == 14) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer: activation rows
+      const uint64_t pol_act = policy_evict_last();
+      int q = 0;
+      uint32_t qph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
+          mbar_expect_tx(&c->op_full[q], act_bytes);
+          tma_load_2d(op_ring + static_cast<size_t>(q) * op_bytes + kOpWeightBytes, &tm_act, &c->op_full[q],
+                      kb * kBlockK, t.row0, pol_act);
+          ++issued;
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
+        }
+      }
+      const long long first = issued > num_operand ? issued - num_operand : 0;
+      for (long long i = first; i < issued; ++i) {  // completes once the converters arrived too; bounded
+        if (!mbar_wait_plain(&c->op_full[i % num_operand], static_cast<uint32_t>((i / num_operand) & 1))) break;
+      }
+    }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
-      int p = 0, q = 0, acc = 0;
-      uint32_t pph = 0, qph = 0, acc_phase = 0;
+      int q = 0, acc = 0;
+      uint32_t qph = 0, acc_phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
@@ -165,11 +194,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
         const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
         const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&c->packed_full[p], pph, &c->abort, status) ||
-              !mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
+          if (!mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t w_addr = smem_u32(op_ring + static_cast<size_t>(q) * kOpBytes);
-          const uint32_t a_addr = smem_u32(packed_ring + static_cast<size_t>(p) * packed_bytes + kWordsBytes);
+          const uint32_t w_addr = smem_u32(op_ring + static_cast<size_t>(q) * op_bytes);
+          const uint32_t a_addr = w_addr + kOpWeightBytes;
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
@@ -178,8 +206,6 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
             if (kGateUp) umma(d_up, umma_desc(w_addr + kWTileBytes + k * kUmmaK * 2), bdesc, idesc, acc_flag);
           }
           umma_commit(&c->op_empty[q]);
-          umma_commit(&c->packed_empty[p]);
-          if (++p == num_packed) { p = 0; pph ^= 1u; }
           if (++q == num_operand) { q = 0; qph ^= 1u; }
         }
         if (!ok) break;
@@ -203,15 +229,16 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
-      mbar_arrive(&c->tmem_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
-    // ------------------------------------------------------------------ converter warps
+    // ------------------------------------------------------------------ converter warps (6..13)
     const int tid = threadIdx.x - 192;
     const int row = tid & 127, half = tid >> 7;
-    // gate/up: half 0 converts the gate tile, half 1 the up tile, a whole row each (8 words);
-    // down: both halves share the one tile, four words each.
+    // gate/up: half 0 converts the gate tile, half 1 the up tile, eight words per 64 K each;
+    // down: both halves share the one tile, four words per 64 K each.
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
     int p = 0, q = 0;
     uint32_t pph = 0, qph = 0;
@@ -222,37 +249,44 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
                        (kGateUp ? half * n_out : 0);
       if (srow >= total_rows) srow = total_rows - 1;  // lanes past the last channel are never stored
       const __nv_bfloat16* srow_ptr = scales + srow * groups;
-      __nv_bfloat16 s_next = srow_ptr[0];
-      __nv_bfloat162 scale2 = __bfloat162bfloat162(s_next);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if ((kb & 1) == 0) {
-          scale2 = __bfloat162bfloat162(s_next);
-          if (kb / 2 + 1 < groups) s_next = srow_ptr[kb / 2 + 1];  // next group's scale, used two k-blocks later
+      __nv_bfloat16 s0 = srow_ptr[0], s1 = srow_ptr[groups > 1 ? 1 : 0];   // the two groups of words stage 0
+      for (int ws = 0; ok && ws < num_ws; ++ws) {
+        const __nv_bfloat162 scale_lo = __bfloat162bfloat162(s0), scale_hi = __bfloat162bfloat162(s1);
+        if (ws + 1 < num_ws) {  // prefetch the next stage's scales while this one is converted
+          s0 = srow_ptr[2 * ws + 2];
+          s1 = srow_ptr[min(2 * ws + 3, groups - 1)];
         }
-        if (!mbar_wait(&c->packed_full[p], pph, &c->abort, status) ||
-            !mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
-        const unsigned char* words = packed_ring + static_cast<size_t>(p) * packed_bytes;
-        unsigned char* dst = op_ring + static_cast<size_t>(q) * kOpBytes + row * 128;
-        if (kGateUp) {
-          const uint4* src = reinterpret_cast<const uint4*>(words + half * kPackedTileBytes + row * 32);
-          dst += half * kWTileBytes;
-          const uint4 w0 = src[0], w1 = src[1];
-          const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        if (!__all_sync(0xffffffffu, mbar_wait(&c->words_full[p], pph, &c->abort, status))) { ok = false; break; }
+        const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes +
+                                     (kGateUp ? half * kWordsTileBytes : 0) + row * 128;
+        const int subs = min(kWordsK, k_dim - ws * kWordsK) / kBlockK;
+        for (int j = 0; j < subs; ++j) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status))) { ok = false; break; }
+          const __nv_bfloat162 scale2 = j < 2 ? scale_lo : scale_hi;
+          unsigned char* dst = op_ring + static_cast<size_t>(q) * op_bytes + row * 128;
+          if (kGateUp) {
+            dst += half * kWTileBytes;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j) ^ (row & 7)) << 4));
+            const uint4 w1 = *reinterpret_cast<const uint4*>(words + (((2 * j + 1) ^ (row & 7)) << 4));
+            const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = dequant_word(w[j], scale2);
-        } else {
-          const uint4 w0 = *reinterpret_cast<const uint4*>(words + row * 32 + half * 16);
-          const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
+          } else {
+            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j + half) ^ (row & 7)) << 4));
+            const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(dst + (((half * 4 + j) ^ (row & 7)) << 4)) = dequant_word(w[j], scale2);
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(dst + (((half * 4 + i) ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
-        mbar_arrive(&c->op_full[q]);
-        mbar_arrive(&c->packed_empty[p]);
-        if (++p == num_packed) { p = 0; pph ^= 1u; }
-        if (++q == num_operand) { q = 0; qph ^= 1u; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c->words_empty[p]);
+        if (++p == num_words) { p = 0; pph ^= 1u; }
       }
     }
   }
@@ -266,20 +300,20 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   }
 }
 
-void rings_for(bool gate_up, int token_tile, int* num_packed, int* num_operand, int* smem_bytes) {
-  const int op = (gate_up ? 2 : 1) * static_cast<int>(kWTileBytes);
-  const int packed = (gate_up ? 2 : 1) * static_cast<int>(kPackedTileBytes) + token_tile * 128;
+void rings_for(bool gate_up, int token_tile, int* num_words, int* num_operand, int* smem_bytes) {
+  const int op = (gate_up ? 2 : 1) * static_cast<int>(kWTileBytes) + token_tile * 128;
+  const int words = (gate_up ? 2 : 1) * static_cast<int>(kWordsTileBytes);
   const int budget = kSmemLimit - kCtrlBytes - 1024;
-  int q = gate_up ? 3 : 4;
-  int p = (budget - q * op) / packed;
-  while (p < 3 && q > 2) {
-    --q;
-    p = (budget - q * op) / packed;
+  int q = 3;
+  while (q > 2 && budget - q * op < 2 * words) --q;
+  int p = (budget - q * op) / words;
+  if (p > kMaxWords) {  // spare room goes to the operand ring
+    p = kMaxWords;
+    while (q < kMaxOperand && budget - (q + 1) * op >= p * words) ++q;
   }
-  if (p > kMaxPacked) p = kMaxPacked;
-  *num_packed = p;
+  *num_words = p;
   *num_operand = q;
-  *smem_bytes = kCtrlBytes + 1024 + q * op + p * packed;
+  *smem_bytes = kCtrlBytes + 1024 + q * op + p * words;
 }
 
 template <bool kGateUp>
@@ -308,7 +342,7 @@ int configure_w4(B200MoePlan& p) {
   rings_for(true, p.token_tile, &p.w4_packed_gate_up, &p.w4_operand_gate_up, &p.w4_smem_gate_up);
   rings_for(false, p.token_tile, &p.w4_packed_down, &p.w4_operand_down, &p.w4_smem_down);
   if (p.w4_packed_gate_up < 2 || p.w4_packed_down < 2) {
-    set_error("token_tile %d leaves fewer than 2 packed stages", p.token_tile);
+    set_error("token_tile %d leaves fewer than 2 stages of packed words", p.token_tile);
     return B200MOE_ERR_INVALID;
   }
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_w4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -1,7 +1,9 @@
 // Router on the tensor cores: logits[token][expert] = x . Wr^T as one tcgen05
-// GEMM per 128-token tile (tokens on the TMEM lanes, experts on the columns), then
-// softmax + top-k + renormalisation by the thread that owns the token's lane -
-// no cross-thread exchange: the whole row of logits is that lane's TMEM row.
+// GEMM per 128-token tile (tokens on the TMEM lanes, experts on the columns). The
+// epilogue warps copy the FP32 logits from tensor memory to shared memory (reusing the
+// drained operand stages), then sixteen warps take rows in turn: the 32 lanes share one
+// row's experts, softmax by warp reductions, top-k by k rounds of warp arg-max done with
+// integer warp reductions (redux.sync) on order-preserving keys of the logits.
 //
 // Formula: scripts/capture_qwen3_moe_layer0.py:583-586 of the reference (FP32
 // softmax, top-k, divide by the sum of the k). The k experts are taken in
@@ -17,7 +19,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+constexpr int kRowWarps = 16;      // warps 2..17 work on rows; the first four of them also read TMEM
+constexpr int kThreads = 64 + kRowWarps * 32;  // warp 0 TMA, warp 1 MMA + TMEM owner
 constexpr int kMaxStages = 8;
 constexpr int kTileTokens = 128;   // UMMA M
 constexpr int kBlockK = 64;
@@ -108,62 +111,92 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       if (!ok) mbar_wait_plain(&c->tmem_full, 0);
     }
   } else {
-    const int quarter = warp & 3;
-    const bool ready = __all_sync(0xffffffffu, mbar_wait(&c->tmem_full, 0, &c->abort, status));
-    if (ready) {
-      tc_fence_after();
-      const int token = t0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      uint32_t v[16];
-      float m = -INFINITY;
-      for (int c0 = 0; c0 < e_pad; c0 += 16) {
-        tmem_ld16(taddr + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < E) m = fmaxf(m, __uint_as_float(v[j]));
-      }
-      float sum = 0.0f;
-      for (int c0 = 0; c0 < e_pad; c0 += 16) {
-        tmem_ld16(taddr + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < E) sum += expf(__uint_as_float(v[j]) - m);
-      }
-      float prev_v = INFINITY, total = 0.0f;
-      int prev_e = -1;
-      const bool live = token < T;
-      IdT* my_ids = ids + static_cast<size_t>(live ? token : 0) * K;
-      float* my_rw = rw + static_cast<size_t>(live ? token : 0) * K;
-      for (int k = 0; k < K; ++k) {
-        float best_v = -INFINITY;
-        int best_e = 0x7fffffff;
+    // ---------------------------------------------------------------- epilogue: warps 2..9
+    const int ld = e_pad + 1;                       // row stride in floats: conflict-free column writes
+    float* logits = reinterpret_cast<float*>(stages);   // [128][ld], aliases the drained operand stages
+    bool ready = true;
+    if (warp < 6) {
+      const int quarter = warp & 3;                 // the TMEM lane quarter this warp may read
+      ready = __all_sync(0xffffffffu, mbar_wait(&c->tmem_full, 0, &c->abort, status));
+      if (ready) {
+        tc_fence_after();
+        const int r = quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         for (int c0 = 0; c0 < e_pad; c0 += 16) {
+          uint32_t v[16];
           tmem_ld16(taddr + c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float l = __uint_as_float(v[j]);
-            const int e = c0 + j;
-            const bool after_prev = l < prev_v || (l == prev_v && e > prev_e);
-            if (e < E && after_prev && (l > best_v || best_e == 0x7fffffff)) { best_v = l; best_e = e; }
+          for (int j = 0; j < 16; ++j) logits[r * ld + c0 + j] = __uint_as_float(v[j]);
+        }
+      } else {
+        c->abort = 1;  // tell the row workers not to touch the logits
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kRowWarps * 32) : "memory");  // TMEM readers -> row workers
+    if (*reinterpret_cast<volatile int*>(&c->abort) == 0) {
+      const int rows_live = min(kTileTokens, T - t0);
+      const int per_lane = e_pad / 32 + ((e_pad % 32) ? 1 : 0);   // <= 8 experts per lane
+      for (int r = warp - 2; r < rows_live; r += kRowWarps) {
+        // key(x): unsigned, monotonic in x; 0 is below every finite logit and marks "absent / taken"
+        uint32_t key[8];
+        uint32_t kmax_local = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = j * 32 + lane;
+          uint32_t u = 0;
+          if (j < per_lane && e < E) {
+            u = __float_as_uint(logits[r * ld + e]);
+            u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;
+          }
+          key[j] = u;
+          kmax_local = max(kmax_local, u);
+        }
+        const uint32_t kmax = __reduce_max_sync(0xffffffffu, kmax_local);
+        const float m = __uint_as_float((kmax >> 31) ? (kmax ^ 0x80000000u) : ~kmax);
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (key[j]) {
+            const uint32_t u = key[j];
+            sum += expf(__uint_as_float((u >> 31) ? (u ^ 0x80000000u) : ~u) - m);
           }
         }
-        if (best_e >= E) { best_e = min(k, E - 1); best_v = -INFINITY; }  // NaN logits: stay in range
-        prev_v = best_v;
-        prev_e = best_e;
-        const float p = expf(best_v - m) / sum;
-        total += p;
-        if (live) {
-          my_ids[k] = static_cast<IdT>(best_e);
-          my_rw[k] = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        uint32_t my_key = 0;
+        int my_e = 0;
+        for (int k = 0; k < K; ++k) {
+          uint32_t best = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) best = max(best, key[j]);
+          const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+          int cand = 0x7fffffff;                     // lowest expert index holding the top key
+#pragma unroll
+          for (int j = 7; j >= 0; --j)
+            if (key[j] == top) cand = j * 32 + lane;
+          int be = __reduce_min_sync(0xffffffffu, top ? cand : 0x7fffffff);
+          if (be >= E) be = min(k, E - 1);           // row exhausted (NaNs / K > finite entries): stay in range
+          const int taken = (be & 31) == lane ? (be >> 5) : -1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) key[j] = j == taken ? 0u : key[j];
+          if (lane == k) { my_key = top; my_e = be; }
+        }
+        float p = 0.0f;
+        if (lane < K && my_key)
+          p = expf(__uint_as_float((my_key >> 31) ? (my_key ^ 0x80000000u) : ~my_key) - m) / sum;
+        float total = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane < K) {
+          const size_t o = static_cast<size_t>(t0 + r) * K + lane;
+          ids[o] = static_cast<IdT>(my_e);
+          rw[o] = p / total;
         }
       }
-      if (live)
-        for (int k = 0; k < K; ++k) my_rw[k] = my_rw[k] / total;
     }
   }
+
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
