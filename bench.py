@@ -211,6 +211,46 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
     }
 
 
+def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world):
+    """Expert-parallel layer: this rank owns E/world experts and `tokens` tokens; NCCL all-to-all between ranks."""
+    from llm_gpu_kernels_b200.moe_ep import expert_range, prepare_ep_moe
+    wr, gate_up, down = weights_cpu
+    e, h, k = QWEN["experts"], QWEN["hidden"], QWEN["topk"]
+    lo, hi = expert_range(rank, world, e)
+    x = x_host.to(dev)
+    ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
+    rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
+    ep = prepare_ep_moe(x, gate_up[lo:hi].contiguous().to(dev), down[lo:hi].contiguous().to(dev), ids, rw,
+                        experts=e, router_weight=wr.to(dev))
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(max(3, warmup)):
+        ep.run()
+    torch.cuda.synchronize(dev)
+    ep.check_inputs()
+
+    def barrier():
+        torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    barrier()
+    ms = event_ms(ep.run, steps, stream)
+    x_pinned = x_host.clone().pin_memory()
+    out_pinned = torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_pinned, non_blocking=True)
+        out_pinned.copy_(ep.run(), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_ms = event_ms(e2e_step, steps, stream)
+    torch.cuda.synchronize(dev)
+    launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
+    return {"ms": ms, "ms_e2e": e2e_ms, "rows_received": ep.stats.rows_received, "launches": launches,
+            "token_tile": ep.backend.expert_plan.token_tile}
+
+
 def cpu_baseline(tokens, weights_cpu, x_cpu, repeats):
     """Oracle port (router + FP32 expert loop) on the host cores; best of `repeats` after one warm-up."""
     from oracle import moe_oracle as O
@@ -305,22 +345,50 @@ def main():
         wr_d, gate_up_d, down_d = (t.to(dev) for t in weights_cpu)
 
     results = {}
+    ep = None
     with ClockSampler(local_rank) as clocks:
-        for tokens in sorted(xs):
-            results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
-                                           args.warmup, peaks, dist_ctx, packed=packed)
-    head = results[args.tokens]
-
-    # every rank runs the same full layer on its own batch (replicas); max over ranks
-    ms, e2e_ms = head["ms_graph"], head["ms_e2e"]
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-    if rank != 0:
         if world > 1:
-            torch.distributed.destroy_process_group()
+            # weak scaling: every rank brings `--tokens` tokens of its own and owns E/world experts
+            gx = torch.Generator().manual_seed(1000 + rank)
+            x_rank = torch.randn(args.tokens, QWEN["hidden"], generator=gx).bfloat16()
+            ep = bench_ep(args.tokens, weights_cpu, x_rank, dev, args.steps, args.warmup, rank, world)
+        else:
+            for tokens in sorted(xs):
+                results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
+                                               args.warmup, peaks, dist_ctx, packed=packed)
+    if world > 1:
+        t = torch.tensor([ep["ms"], ep["ms_e2e"], float(ep["rows_received"])], device=dev, dtype=torch.float64)
+        tmax, tsum = t.clone(), t.clone()
+        torch.distributed.all_reduce(tmax, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(tsum, op=torch.distributed.ReduceOp.SUM)
+        if rank == 0:
+            ms, e2e_ms, max_rows = tmax.tolist()
+            mean_rows = tsum.tolist()[2] / world
+            line = {
+                "metric": METRIC, "value": world * args.tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"Qwen3-30B-A3B MoE layer forward, expert-parallel: {args.tokens} tokens per GPU, "
+                                       f"E128 split {128 // world} experts per GPU, H2048 I768 top-8, BF16",
+                           "timing": "eager forwards (one host read of the all-to-all split sizes per step), CUDA events, "
+                                     "max over ranks",
+                           "l2": "inputs larger than L2: each rank streams its experts' weights "
+                                 f"({1.2 / world:.2f} GB) per step",
+                           "parallelism": f"ep{world}", "token_tile": ep["token_tile"],
+                           "rows_received_max": max_rows, "rows_received_mean": mean_rows},
+                "e2e": {"value": world * args.tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": args.tokens * QWEN["hidden"] * 2,
+                        "d2h_bytes_per_step": args.tokens * QWEN["hidden"] * 2, "ms_per_step": e2e_ms},
+                "gpu_launches": args.steps * ep["launches"],
+                "clocks": clocks.summary(),
+                "roofline": {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
+                             "traffic": None, "note": "per-kernel roofline is reported by the 1-GPU run"},
+            }
+            print(json.dumps(line), flush=True)
+        torch.distributed.destroy_process_group()
         return
+    head = results[args.tokens]
+    ms, e2e_ms = head["ms_graph"], head["ms_e2e"]
 
     cpu = None
     if not args.no_cpu_baseline:

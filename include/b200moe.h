@@ -63,7 +63,9 @@ typedef struct {
   int32_t schedule;       /* B200MOE_SCHEDULE_* */
   int32_t token_tile;     /* rows of one expert handled by one tile; 0 = choose from T*K/E */
   int32_t use_router;     /* 1: ids / routing_weights are written by the router each forward */
-  int32_t reserved[5];
+  int32_t route_only;     /* 1: no expert weights: forward = router + dispatch; combine reads down_output
+                             filled by the caller (the token-owning side of expert parallelism) */
+  int32_t reserved[4];
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned
@@ -111,6 +113,8 @@ typedef struct {
   void* down_output;
   void* status;
   void* scratch;
+  const void* valid_routes;    /* optional device int32: only the first *valid_routes routes exist this forward
+                                  (the rest of the fixed-capacity buffers is padding); NULL = all T*K */
 } B200MoeBuffers;
 
 /* ABI version of the loaded library. */

@@ -31,7 +31,7 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_STATE = -1, -2, -3, -4
 class Shape(ctypes.Structure):
     _fields_ = [(name, ctypes.c_int32) for name in (
         "tokens", "experts", "topk", "hidden", "intermediate", "ids_are_int64", "gate_up_format",
-        "down_format", "schedule", "token_tile", "use_router")] + [("reserved", ctypes.c_int32 * 5)]
+        "down_format", "schedule", "token_tile", "use_router", "route_only")] + [("reserved", ctypes.c_int32 * 4)]
 
 
 WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "ranks",
@@ -49,7 +49,7 @@ INPUT_BUFFERS = ("x", "router_weight", "gate_up", "gate_up_scales", "down", "dow
 
 
 class Buffers(ctypes.Structure):
-    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS]
+    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS + ("valid_routes",)]
 
 
 class DispatchArgs(ctypes.Structure):

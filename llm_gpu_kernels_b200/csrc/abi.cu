@@ -224,13 +224,13 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.mapping = R * 4;
   w.ranks = R * 4;
   w.grouped_input = R * H * 2;
-  w.activated = R * I * 2;
+  w.activated = s.route_only ? 0 : R * I * 2;
   w.down_output = R * H * 2;
   w.status = 4;
   w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 1) * 4);
   w.token_tile = tile;
   w.schedule = schedule;
-  w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + 3;
+  w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + (s.route_only ? 0 : 3);
   *out = p;
   return B200MOE_OK;
 }
@@ -264,11 +264,15 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
   }
   if (s.tokens > 0) {
     struct Named { const void* ptr; const char* name; };
-    const Named needed[] = {{b->x, "x"}, {b->gate_up, "gate_up"}, {b->down, "down"}, {b->ids, "ids"},
+    if (!s.route_only && (!b->gate_up || !b->down || !b->activated)) {
+      set_error("gate_up, down and activated buffers are required unless the plan is route_only");
+      return B200MOE_ERR_INVALID;
+    }
+    const Named needed[] = {{b->x, "x"}, {b->ids, "ids"},
                             {b->routing_weights, "routing_weights"}, {b->output, "output"}, {b->counts, "counts"},
                             {b->offsets, "offsets"}, {b->cursors, "cursors"}, {b->tasks, "tasks"},
                             {b->mapping, "mapping"}, {b->ranks, "ranks"}, {b->grouped_input, "grouped_input"},
-                            {b->activated, "activated"}, {b->down_output, "down_output"}, {b->status, "status"},
+                            {b->down_output, "down_output"}, {b->status, "status"},
                             {b->scratch, "scratch"}};
     for (const Named& n : needed) {
       if (!n.ptr) {
@@ -310,7 +314,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
       if (rc) return rc;
     }
   }
-  if (s.tokens > 0 && p->schedule == B200MOE_SCHEDULE_TCGEN05) {
+  if (s.tokens > 0 && p->schedule == B200MOE_SCHEDULE_TCGEN05 && !s.route_only) {
     const void* aligned16[] = {b->gate_up, b->down, b->grouped_input, b->activated};
     for (const void* ptr : aligned16)
       if (reinterpret_cast<uintptr_t>(ptr) % 16) {
@@ -364,6 +368,10 @@ int b200moe_gate_up(B200MoePlan* p, void* stream) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
+  if (p->shape.route_only) {
+    set_error("a route_only plan has no expert stages");
+    return B200MOE_ERR_STATE;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_gate_up_generic(*p, s), "gate_up launch");
   return check_cuda(is_w4(p->shape.gate_up_format) ? launch_gate_up_w4(*p, s) : launch_gate_up_tc(*p, s),
@@ -374,6 +382,10 @@ int b200moe_down(B200MoePlan* p, void* stream) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
+  if (p->shape.route_only) {
+    set_error("a route_only plan has no expert stages");
+    return B200MOE_ERR_STATE;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
   return check_cuda(is_w4(p->shape.down_format) ? launch_down_w4(*p, s) : launch_down_tc(*p, s), "down launch");
@@ -390,6 +402,7 @@ int b200moe_forward(B200MoePlan* p, void* stream) {
   int rc;
   if ((rc = b200moe_router(p, stream))) return rc;
   if ((rc = b200moe_dispatch(p, stream))) return rc;
+  if (p && p->shape.route_only) return B200MOE_OK;  // experts run elsewhere; the caller combines later
   if ((rc = b200moe_gate_up(p, stream))) return rc;
   if ((rc = b200moe_down(p, stream))) return rc;
   return b200moe_combine(p, stream);

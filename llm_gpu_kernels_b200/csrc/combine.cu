@@ -16,8 +16,10 @@ constexpr int kThreads = 64;  // small blocks: T * H/512 of them even for a hand
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict__ mapping,
-               const float* __restrict__ rw, __nv_bfloat16* __restrict__ out, int H, int K) {
+               const float* __restrict__ rw, __nv_bfloat16* __restrict__ out, const int* __restrict__ valid_routes,
+               int H, int K) {
   const int token = blockIdx.x;
+  if (valid_routes && token * K >= *valid_routes) return;  // padding rows of a fixed-capacity buffer
   __shared__ int s_pos[32];
   __shared__ float s_w[32];
   if (threadIdx.x < K) {
@@ -83,13 +85,13 @@ cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s) {
   if (vec) {
     dim3 grid(sh.tokens, (sh.hidden / 8 + kThreads - 1) / kThreads);
     combine_kernel<true><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
-                                                   static_cast<const float*>(p.buf.routing_weights), o, sh.hidden,
-                                                   sh.topk);
+                                                   static_cast<const float*>(p.buf.routing_weights), o,
+                                                   static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
   } else {
     dim3 grid(sh.tokens, (sh.hidden + kThreads - 1) / kThreads);
     combine_kernel<false><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
-                                                    static_cast<const float*>(p.buf.routing_weights), o, sh.hidden,
-                                                    sh.topk);
+                                                    static_cast<const float*>(p.buf.routing_weights), o,
+                                                    static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
   }
   return cudaPeekAtLastError();
 }

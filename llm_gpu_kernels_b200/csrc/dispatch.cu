@@ -36,8 +36,9 @@ constexpr int kMaxExperts = 256;
 template <typename IdT>
 __global__ void __launch_bounds__(kThreads)
 dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
-                      int* __restrict__ hist, int* __restrict__ flags, int R, int E, int warp_routes,
-                      int partitions) {
+                      int* __restrict__ hist, int* __restrict__ flags, const int* __restrict__ valid_routes, int R,
+                      int E, int warp_routes, int partitions) {
+  const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
   __shared__ int warp_hist[kWarps][kMaxExperts];
   __shared__ int block_flags;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -51,12 +52,12 @@ dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
     const int end = min(R, begin + warp_routes);
     for (int base = begin; base < end; base += 32) {
       const int q = base + lane;
-      const bool in = q < end;
-      long long id = in ? static_cast<long long>(ids[q]) : -1;
-      const float w = in ? rw[q] : 0.0f;
-      const bool valid = in && id >= 0 && id < E;
-      if (in && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
-      if (in && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;  // false for NaN too
+      const bool in = q < end, live = in && q < r_eff;
+      long long id = live ? static_cast<long long>(ids[q]) : -1;
+      const float w = live ? rw[q] : 0.0f;
+      const bool valid = live && id >= 0 && id < E;
+      if (live && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
+      if (live && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;  // false for NaN too
       const int key = valid ? static_cast<int>(id) : E;  // E = "no expert"
       const unsigned peers = __match_any_sync(0xffffffffu, key);
       const int below = __popc(peers & ((1u << lane) - 1u));
@@ -148,7 +149,9 @@ __global__ void __launch_bounds__(1024)
 dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
                       int* __restrict__ mapping, int* __restrict__ counts, int* __restrict__ offsets,
                       int* __restrict__ cursors, int* __restrict__ tasks, int* __restrict__ status,
-                      int* __restrict__ router_flag, int R, int E, int warp_routes, int token_tile) {
+                      int* __restrict__ router_flag, const int* __restrict__ valid_routes, int R, int E,
+                      int warp_routes, int token_tile) {
+  const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
   __shared__ int warp_hist[32][kMaxExperts];
   __shared__ int s_off[kMaxExperts];
   __shared__ int s_scan[16];
@@ -161,12 +164,12 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
   int my_flags = 0;
   for (int base = begin; base < end; base += 32) {
     const int q = base + lane;
-    const bool in = q < end;
-    const long long id = in ? static_cast<long long>(ids[q]) : -1;
-    const float w = in ? rw[q] : 0.0f;
-    const bool valid = in && id >= 0 && id < E;
-    if (in && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
-    if (in && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;
+    const bool in = q < end, live = in && q < r_eff;
+    const long long id = live ? static_cast<long long>(ids[q]) : -1;
+    const float w = live ? rw[q] : 0.0f;
+    const bool valid = live && id >= 0 && id < E;
+    if (live && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
+    if (live && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;
     const int key = valid ? static_cast<int>(id) : E;
     const unsigned peers = __match_any_sync(0xffffffffu, key);
     const int below = __popc(peers & ((1u << lane) - 1u));
@@ -207,7 +210,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
   for (int base = begin; base < end; base += 32) {
     const int q = base + lane;
     if (q >= end) continue;
-    const long long id = static_cast<long long>(ids[q]);
+    const long long id = q < r_eff ? static_cast<long long>(ids[q]) : -1;
     int rank = -1, pos = -1;
     if (id >= 0 && id < E) {
       rank = ranks[q] + warp_hist[warp][id];  // ranks[q] was written by this same thread above
@@ -243,11 +246,13 @@ __global__ void __launch_bounds__(kThreads)
 dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restrict__ ids,
                         const int* __restrict__ hist, const int* __restrict__ offsets,
                         int* __restrict__ ranks, int* __restrict__ mapping,
-                        __nv_bfloat16* __restrict__ grouped, int R, int E, int H, int K, int warp_routes) {
+                        __nv_bfloat16* __restrict__ grouped, const int* __restrict__ valid_routes, int R, int E,
+                        int H, int K, int warp_routes) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = blockIdx.x * kWarps + warp;
   if (q >= R) return;
-  const long long id = static_cast<long long>(ids[q]);
+  const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;
+  const long long id = q < r_eff ? static_cast<long long>(ids[q]) : -1;
   const bool valid = id >= 0 && id < E;
   int pos = -1;
   if (lane == 0) {  // one lane owns the read-modify-write of ranks[q]
@@ -282,6 +287,7 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   int* flags = hist + static_cast<size_t>(p.partitions) * E;
   int* ranks = static_cast<int*>(p.buf.ranks);
   auto* rw = static_cast<const float*>(p.buf.routing_weights);
+  auto* valid = static_cast<const int*>(p.buf.valid_routes);
   if (p.dispatch_fused) {
     int* router_flag = hist + router_flag_index(p);
     auto* counts = static_cast<int*>(p.buf.counts);
@@ -292,12 +298,12 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     auto* mapping = static_cast<int*>(p.buf.mapping);
     if (sh.ids_are_int64) {
       dispatch_fused_kernel<long long><<<1, 1024, 0, s>>>(static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
-                                                          counts, offsets, cursors, tasks, status, router_flag, R, E,
-                                                          p.warp_routes, p.token_tile);
+                                                          counts, offsets, cursors, tasks, status, router_flag, valid, R,
+                                                          E, p.warp_routes, p.token_tile);
     } else {
       dispatch_fused_kernel<int><<<1, 1024, 0, s>>>(static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
-                                                    offsets, cursors, tasks, status, router_flag, R, E, p.warp_routes,
-                                                    p.token_tile);
+                                                    offsets, cursors, tasks, status, router_flag, valid, R, E,
+                                                    p.warp_routes, p.token_tile);
     }
     dispatch_copy_kernel<<<(R + kWarps - 1) / kWarps, kThreads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p.buf.x), mapping, static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
@@ -306,10 +312,10 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   }
   if (sh.ids_are_int64) {
     dispatch_count_kernel<long long><<<blocks, kThreads, 0, s>>>(
-        static_cast<const long long*>(p.buf.ids), rw, ranks, hist, flags, R, E, p.warp_routes, p.partitions);
+        static_cast<const long long*>(p.buf.ids), rw, ranks, hist, flags, valid, R, E, p.warp_routes, p.partitions);
   } else {
     dispatch_count_kernel<int><<<blocks, kThreads, 0, s>>>(
-        static_cast<const int*>(p.buf.ids), rw, ranks, hist, flags, R, E, p.warp_routes, p.partitions);
+        static_cast<const int*>(p.buf.ids), rw, ranks, hist, flags, valid, R, E, p.warp_routes, p.partitions);
   }
   dispatch_scan_kernel<<<1, kMaxExperts, 0, s>>>(
       hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
@@ -321,11 +327,11 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   if (sh.ids_are_int64) {
     dispatch_permute_kernel<long long><<<pblocks, kThreads, 0, s>>>(
         x, static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
-        static_cast<int*>(p.buf.mapping), grouped, R, E, sh.hidden, sh.topk, p.warp_routes);
+        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
   } else {
     dispatch_permute_kernel<int><<<pblocks, kThreads, 0, s>>>(
         x, static_cast<const int*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
-        static_cast<int*>(p.buf.mapping), grouped, R, E, sh.hidden, sh.topk, p.warp_routes);
+        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
   }
   return cudaPeekAtLastError();
 }

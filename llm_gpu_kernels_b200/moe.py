@@ -83,6 +83,7 @@ class PreparedMoE:
     gate_up_scales: torch.Tensor = None  # set when gate_up holds packed W4G128 words
     down_scales: torch.Tensor = None     # set when down holds packed W4G128 words
     packed: object = None                # the PackedGateUp the plan was prepared from (reference W4Workspace.packed)
+    valid_routes: torch.Tensor = None    # optional device int32: routes beyond it are padding this forward
     schedule: str = ""
     token_tile: int = 0
     launches: tuple = ()
@@ -158,15 +159,23 @@ def _packed_input(words, scales, name):
         raise ValueError("16-byte input alignment required")
 
 
-def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales=None, down_scales=None):
+def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales=None, down_scales=None,
+              route_only_experts=None):
     _input(x, 2)
-    if gate_up_scales is None:
+    if route_only_experts is not None:
+        # token-owning side of expert parallelism: no expert weights on this plan
+        e, h, intermediate = int(route_only_experts), x.shape[1], 64
+        gate_up_shape = (e, 2 * intermediate, h)
+        gate_up = down = None
+    elif gate_up_scales is None:
         _input(gate_up, 3)
         gate_up_shape = tuple(gate_up.shape)
     else:
         _packed_input(gate_up, gate_up_scales, "gate_up")
         gate_up_shape = (gate_up.shape[0], gate_up.shape[1], gate_up.shape[2] * 8)
-    if down_scales is None:
+    if route_only_experts is not None:
+        pass
+    elif down_scales is None:
         _input(down, 3)
         e, h, intermediate = down.shape
     else:
@@ -181,7 +190,8 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
             or routing_weights.dtype != torch.float32):
         raise ValueError("expected CUDA IDs[T,topk<=32] and FP32 weights of identical shape")
     extra = [t for t in (gate_up_scales, down_scales) if t is not None]
-    if any(t.device != x.device or not t.is_contiguous() for t in (gate_up, down, ids, routing_weights, *extra)):
+    weights = [t for t in (gate_up, down) if t is not None]
+    if any(t.device != x.device or not t.is_contiguous() for t in (*weights, ids, routing_weights, *extra)):
         raise ValueError("all MoE tensors must be contiguous and on the same CUDA device")
     r = ids.numel()
     if r >= 2**31 or r * max(h, 2 * intermediate) >= 2**31:
@@ -196,14 +206,18 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 
 
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
-             token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None):
+             token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
+             route_only_experts=None, valid_routes=None):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
     W4G128 int32 word tensor instead of a BF16 tensor.
     """
     e, h, intermediate = _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales,
-                                   down_scales)
+                                   down_scales, route_only_experts)
+    if valid_routes is not None and (valid_routes.dtype != torch.int32 or valid_routes.numel() != 1
+                                     or valid_routes.device != x.device):
+        raise ValueError("valid_routes must be one int32 on the same device")
     if schedule not in _SCHEDULES:
         raise ValueError(f"unknown schedule {schedule!r}; expected one of auto/generic/tcgen05")
     lib = _native.load()
@@ -214,7 +228,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           gate_up_format=_native.WEIGHTS_BF16 if gate_up_scales is None else _native.WEIGHTS_W4G128,
                           down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
-                          use_router=int(router_weight is not None))
+                          use_router=int(router_weight is not None),
+                          route_only=int(route_only_experts is not None))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -228,11 +243,13 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         plan = PreparedMoE(
             x, gate_up, down, ids, routing_weights, bf16((tokens, h)),
             int32((e,)), int32((e,)), int32((e,)), int32((e + 1,)), int32((r,)),
-            bf16((r, h)), bf16((0, 2 * intermediate)), bf16((r, intermediate)), bf16((r, h)),
+            bf16((r, h)), bf16((0, 2 * intermediate)),
+            bf16((0 if route_only_experts is not None else r, intermediate)), bf16((r, h)),
             int32((1,)), config,
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
-            kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales)
+            kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
+            valid_routes=valid_routes)
         expected = {"output": plan.output, "counts": plan.counts, "offsets": plan.offsets,
                     "cursors": plan.cursors, "tasks": plan.tasks, "mapping": plan.mapping, "ranks": plan.ranks,
                     "grouped_input": plan.grouped_input, "activated": plan.activated,
@@ -244,6 +261,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         buffers = _native.Buffers(
             x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales),
             down=ptr(down), down_scales=ptr(down_scales), ids=ptr(ids), routing_weights=ptr(routing_weights),
+            valid_routes=ptr(valid_routes),
             **{name: ptr(tensor) for name, tensor in expected.items()})
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))

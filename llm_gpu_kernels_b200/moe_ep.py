@@ -1,0 +1,199 @@
+"""Expert-parallel MoE layer over the ranks of one node.
+
+The reference is single-GPU and has nothing here; this is the natural sharding
+of its path: experts are independent, so rank ``r`` of ``G`` owns experts
+``[r*E/G, (r+1)*E/G)`` (their weights only) and its own slice of the tokens.
+One forward on every rank:
+
+ 1. router + ranked dispatch of the local tokens over ALL experts. The
+    dispatch sorts routes by expert, and experts are contiguous per rank, so
+    ``grouped_input`` already is the send buffer, split by destination rank.
+ 2. all-gather of the per-expert counts (G*E int32), one host read of the
+    split sizes, then the all-to-all-v of the routed rows (BF16, NCCL over
+    NVLink) straight into the input buffer of the local expert plan.
+ 3. the local experts run the ordinary fixed-route path (top-1, weight 1) on
+    the received rows; a device scalar tells the kernels how many rows of the
+    fixed-capacity buffers are real this forward.
+ 4. all-to-all-v of the results back, straight into ``down_output`` of the
+    token-owning plan, and its weighted combine in slot order.
+
+No kernel touches another GPU's memory; rows always land in a local buffer
+first. The exchange logic is device-agnostic (``backend`` supplies the compute
+stages), which is how the two-rank CPU tests drive it over gloo.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .moe import _prepare
+from .moe_full_policy import token_tile_for
+
+STATUS_EP_OVERFLOW = 8
+
+
+def expert_range(rank: int, world: int, experts: int):
+    """Contiguous block of experts owned by ``rank``."""
+    if experts % world:
+        raise ValueError("experts must divide evenly over the ranks")
+    per = experts // world
+    return rank * per, (rank + 1) * per
+
+
+def split_sizes(counts_by_peer: torch.Tensor):
+    """Rows per peer from a ``[G, E/G]`` count matrix (host list)."""
+    return [int(v) for v in counts_by_peer.sum(dim=1).tolist()]
+
+
+def received_expert_ids(recv_counts: torch.Tensor, total: int):
+    """Local expert id of every received row.
+
+    Peer ``s`` sends its rows sorted by expert, ``recv_counts[s, e]`` of them for
+    local expert ``e``; the receive buffer is the concatenation over peers.
+    """
+    peers, local = recv_counts.shape
+    pattern = torch.arange(local, dtype=torch.int32, device=recv_counts.device).repeat(peers)
+    return torch.repeat_interleave(pattern, recv_counts.reshape(-1).long(), output_size=total)
+
+
+class CudaBackend:
+    """The compute stages on one GPU: a route-only plan for the local tokens and a
+    fixed-route plan (top-1, capacity rows) over the local experts."""
+
+    def __init__(self, x, gate_up_local, down_local, ids, routing_weights, *, experts, router_weight, capacity,
+                 global_routes, gate_up_scales=None, down_scales=None):
+        device = x.device
+        hidden = x.shape[1]
+        local_experts = gate_up_local.shape[0]
+        self.token_plan = _prepare(x, None, None, ids, routing_weights, router_weight=router_weight,
+                                   route_only_experts=experts)
+        self.recv_x = torch.zeros((capacity, hidden), dtype=torch.bfloat16, device=device)
+        self.recv_ids = torch.zeros((capacity, 1), dtype=torch.int32, device=device)
+        self.recv_rw = torch.ones((capacity, 1), dtype=torch.float32, device=device)
+        self.valid = torch.zeros((1,), dtype=torch.int32, device=device)
+        inter = down_local.shape[2] * (8 if down_scales is not None else 1)
+        tensor_tiles = hidden % 8 == 0 and inter % 8 == 0 and hidden >= 64 and inter >= 64
+        # tile from the global load per expert, not from the (worst-case) capacity
+        tile = token_tile_for(global_routes, experts, 1) if tensor_tiles else 0
+        self.expert_plan = _prepare(self.recv_x, gate_up_local, down_local, self.recv_ids, self.recv_rw,
+                                    token_tile=tile, valid_routes=self.valid,
+                                    gate_up_scales=gate_up_scales, down_scales=down_scales)
+        self.local_experts = local_experts
+
+    # token-owning side
+    def route_and_dispatch(self):
+        self.token_plan.route()
+        self.token_plan.dispatch()
+        return self.token_plan.counts
+
+    @property
+    def send_rows(self):
+        return self.token_plan.grouped_input
+
+    @property
+    def return_rows(self):
+        return self.token_plan.down_output
+
+    def combine(self):
+        self.token_plan.combine()
+        return self.token_plan.output
+
+    # expert-owning side
+    @property
+    def recv_rows(self):
+        return self.recv_x
+
+    def set_received(self, expert_ids, total):
+        self.recv_ids[:total, 0].copy_(expert_ids)
+        self.valid.fill_(total)
+
+    def expert_forward(self):
+        return self.expert_plan.run()
+
+    def status(self):
+        return int(self.token_plan.status.item()) | int(self.expert_plan.status.item())
+
+
+@dataclass
+class ExpertParallelStats:
+    sent: list
+    received: list
+
+    @property
+    def rows_received(self):
+        return sum(self.received)
+
+
+class ExpertParallelMoE:
+    """Prepared expert-parallel layer; ``run()`` returns this rank's ``[T_local, H]`` output."""
+
+    def __init__(self, backend, *, experts, group=None, capacity):
+        self.backend = backend
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.experts = experts
+        self.local_experts = experts // self.world
+        self.capacity = capacity
+        self.stats = None
+        self.status_flags = 0
+
+    def _exchange_rows(self, recv, send, recv_splits, send_splits):
+        # BF16 rows travel as raw bytes (a dtype every backend moves)
+        dist.all_to_all_single(recv.view(torch.uint8), send.view(torch.uint8), recv_splits, send_splits,
+                               group=self.group)
+
+    def run(self):
+        be = self.backend
+        counts = be.route_and_dispatch()                                    # [E] int32, local routes per expert
+        # every rank learns the whole [G, E] count matrix (G*E int32), so all ranks take the same
+        # decision on a capacity overflow without another collective
+        all_counts = torch.empty((self.world * self.experts,), dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(all_counts, counts.contiguous().view(-1), group=self.group)
+        by_owner = all_counts.view(self.world, self.world, self.local_experts)       # [source, owner, expert]
+        send_counts = by_owner[self.rank]                                             # [owner, E/G]
+        recv_counts = by_owner[:, self.rank].contiguous()                             # [source, E/G]
+        per_owner = by_owner.sum(dim=(0, 2)).tolist()                                 # the one host read
+        send_splits, recv_splits = split_sizes(send_counts), split_sizes(recv_counts)
+        n_send, n_recv = sum(send_splits), sum(recv_splits)
+        self.stats = ExpertParallelStats(send_splits, recv_splits)
+        if max(per_owner) > self.capacity:
+            n_recv = int(max(per_owner))
+            self.status_flags |= STATUS_EP_OVERFLOW
+            raise RuntimeError(f"expert-parallel receive capacity exceeded: {n_recv} rows > {self.capacity} "
+                               f"(status {STATUS_EP_OVERFLOW})")
+        self._exchange_rows(be.recv_rows[:n_recv], be.send_rows[:n_send], recv_splits, send_splits)
+        be.set_received(received_expert_ids(recv_counts, n_recv), n_recv)
+        result = be.expert_forward()                                        # [capacity, H], received order
+        self._exchange_rows(be.return_rows[:n_send], result[:n_recv], send_splits, recv_splits)
+        return be.combine()
+
+    def check_inputs(self):
+        flags = self.backend.status() | self.status_flags
+        if flags:
+            raise ValueError(f"invalid runtime MoE inputs: GPU status={flags} "
+                             "(1=IDs, 2=nonfinite weights, 4=kernel wait timeout, 8=EP capacity)")
+
+
+def prepare_ep_moe(x, gate_up_local, down_local, ids, routing_weights, *, experts, router_weight=None, group=None,
+                   capacity=None, gate_up_scales=None, down_scales=None):
+    """Prepare the expert-parallel layer on this rank.
+
+    ``x`` [T_local,H] are this rank's tokens; ``gate_up_local`` / ``down_local`` hold only the
+    experts of :func:`expert_range`; ``ids`` / ``routing_weights`` [T_local,K] are inputs (global expert
+    ids) or, with ``router_weight`` [E,H], outputs. ``capacity`` = rows this rank can receive
+    (default: every route of every rank, assuming equal token counts).
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    lo, hi = expert_range(rank, world, experts)
+    if gate_up_local.shape[0] != hi - lo or down_local.shape[0] != hi - lo:
+        raise ValueError(f"rank {rank} must hold experts [{lo},{hi})")
+    routes = ids.numel()
+    capacity = capacity if capacity is not None else max(1, routes * world)
+    backend = CudaBackend(x, gate_up_local, down_local, ids, routing_weights, experts=experts,
+                          router_weight=router_weight, capacity=capacity, global_routes=max(1, routes * world),
+                          gate_up_scales=gate_up_scales, down_scales=down_scales)
+    return ExpertParallelMoE(backend, experts=experts, group=group, capacity=capacity)

@@ -1,0 +1,74 @@
+"""Expert-parallel path on GPUs: NCCL all-to-all between ranks, each rank running the CUDA
+plans. One-rank case runs in-process on any B200; the two-rank case needs two GPUs."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as O
+from tests.util import make_inputs, seeded_layer
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_rank(rank, world, port, shape, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from llm_gpu_kernels_b200.moe_ep import expert_range, prepare_ep_moe
+        from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+        t_local, experts, topk, hidden, inter, use_router = shape
+        wr, gate_up, down, x = seeded_layer(5, t_local * world, hidden, inter, experts, wscale=0.05)
+        _, _, _, ids_all, rw_all = make_inputs(t_local * world, experts, topk, 8, 8, seed=6, pattern="hot")
+        lo, hi = expert_range(rank, world, experts)
+        mine = slice(rank * t_local, (rank + 1) * t_local)
+        ids = ids_all[mine].contiguous().to(dev)
+        rw = rw_all[mine].contiguous().to(dev)
+        ep = prepare_ep_moe(x[mine].contiguous().to(dev), gate_up[lo:hi].contiguous().to(dev),
+                            down[lo:hi].contiguous().to(dev), ids, rw, experts=experts,
+                            router_weight=wr.to(dev) if use_router else None)
+        for _ in range(2):
+            out = ep.run()
+        torch.cuda.synchronize()
+        ep.check_inputs()
+        # parity 1: against the FP32 oracle on the routes this rank used
+        ref = O.moe_oracle(x[mine], gate_up, down, ids.cpu(), rw.cpu())
+        m = O.error_metrics(out.float().cpu(), ref)
+        assert m["relative_rms"] <= 5e-3 and m["normalized_max"] <= 8e-3, m
+        # parity 2: bit-identical to the single-GPU plan on the same tokens and routes
+        single = prepare_ranked_moe_launcher(x[mine].contiguous().to(dev), gate_up.to(dev), down.to(dev),
+                                             ids.clone(), rw.clone())
+        assert torch.equal(single.run(), out)
+        # parity 3: the counts of all ranks add up to the global histogram, bit-exact
+        total = ep.backend.token_plan.counts.clone()
+        dist.all_reduce(total)
+        gathered = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(gathered, ids)
+        expect = torch.bincount(torch.cat(gathered).reshape(-1).long().cpu(), minlength=experts)
+        assert torch.equal(total.cpu().long(), expect)
+        result[rank] = (m["relative_rms"], ep.stats.rows_received)
+    finally:
+        dist.destroy_process_group()
+
+
+SHAPES = [(96, 16, 4, 256, 128, False), (50, 8, 2, 128, 64, True), (33, 4, 2, 72, 40, True)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_one_rank_expert_parallel(shape):
+    result = mp.Manager().dict()
+    mp.spawn(_run_rank, args=(1, 29741, shape, result), nprocs=1, join=True)
+    assert result[0][1] == shape[0] * shape[2]
+
+
+@pytest.mark.parametrize("shape", [(96, 16, 4, 256, 128, True), (1024, 128, 8, 2048, 768, True)])
+def test_two_rank_expert_parallel(shape):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    result = mp.Manager().dict()
+    mp.spawn(_run_rank, args=(2, 29743, shape, result), nprocs=2, join=True)
+    assert sum(v[1] for v in result.values()) == 2 * shape[0] * shape[2]
