@@ -64,8 +64,12 @@ typedef struct {
   int32_t token_tile;     /* rows of one expert handled by one tile; 0 = choose from T*K/E */
   int32_t use_router;     /* 1: ids / routing_weights are written by the router each forward */
   int32_t route_only;     /* 1: no expert weights: forward = router + dispatch; combine reads down_output
-                             filled by the caller (the token-owning side of expert parallelism) */
-  int32_t reserved[4];
+                             filled by the caller (the token-owning side of expert parallelism);
+                             2: the same, and dispatch does not copy rows (grouped_input may be NULL) */
+  int32_t external_dispatch; /* 1: rows arrive already grouped by expert and counts / offsets / tasks are
+                             written by someone else (the expert-owning side of expert parallelism):
+                             forward = gate_up + down on grouped_input; x / ids / weights / output unused */
+  int32_t reserved[3];
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned
@@ -200,6 +204,62 @@ typedef struct {
  *    with events. Nothing needs to be cleared by the caller between calls.
  *  - It calls no cudaMalloc / cudaFree or other allocating routine. */
 int b200moe_dispatch_static(const B200MoeDispatchArgs* args, void* cuda_stream);
+
+/* ---- expert parallelism over peer memory (no counterpart in the single-GPU reference) ----
+ * Ranks of one node, one process per GPU. Rank r owns experts [r*E/G, (r+1)*E/G) and a slice of the
+ * tokens. The buffers named *_peers are allocated with b200moe_peer_alloc() on every rank and opened on
+ * the others with b200moe_peer_export()/import(): entry g is the address of rank g's buffer as seen
+ * from this process (entry `rank` is the local one). Rows cross NVLink by plain stores from the
+ * dispatch / return kernels; nothing is staged and the host never reads a count. */
+#define B200MOE_EP_MAX_RANKS 8
+
+typedef struct {
+  int32_t rank, world;            /* 1 <= world <= 8, experts % world == 0 */
+  int32_t experts, topk, hidden;  /* global E, K, H */
+  int32_t tokens;                 /* tokens of this rank */
+  int32_t capacity;               /* rows each rank's receive buffer holds */
+  int32_t token_tile;             /* tile of the expert plan (for its `tasks` prefix) */
+  int32_t ids_are_int64;
+  int32_t reserved[3];
+  /* token-owning side (local) */
+  const void* x;                  /* [tokens,H] bf16 */
+  const void* ids;                /* [tokens,K] */
+  const void* ranks;              /* [tokens*K] int32, from the route-only plan's dispatch */
+  const void* counts;             /* [E] int32, from the route-only plan's dispatch */
+  /* expert-owning side (local): metadata of the external_dispatch plan, written here */
+  void* expert_counts;            /* [E/G] int32 */
+  void* expert_offsets;           /* [E/G] int32 */
+  void* expert_tasks;             /* [E/G+1] int32 */
+  void* expert_rows;              /* [1] int32: rows received this forward */
+  const void* expert_output;      /* [capacity,H] bf16: down_output of the expert plan, grouped order */
+  void* tables;                   /* local int32 scratch: b200moe_ep_table_ints() entries */
+  void* status;                   /* [1] int32 status word of the token plan */
+  /* peer-visible buffers, one address per rank */
+  void* recv_rows_peers[B200MOE_EP_MAX_RANKS];   /* [capacity,H] bf16: grouped_input of the expert plan */
+  void* return_rows_peers[B200MOE_EP_MAX_RANKS]; /* [tokens*K,H] bf16: down_output of the token plan */
+  void* all_counts_peers[B200MOE_EP_MAX_RANKS];  /* [G,E] int32 */
+  void* flags_peers[B200MOE_EP_MAX_RANKS];       /* [4*8] int32 barrier flags + [4] local epochs */
+} B200MoeEpArgs;
+
+/* int32 entries of B200MoeEpArgs.tables for a given world / experts. */
+size_t b200moe_ep_table_ints(int32_t world, int32_t experts);
+
+/* cudaMalloc'd, zeroed device memory that other processes of the node may open. */
+int b200moe_peer_alloc(size_t bytes, void** ptr);
+int b200moe_peer_free(void* ptr);
+int b200moe_peer_export(void* ptr, unsigned char handle[64]);
+int b200moe_peer_import(const unsigned char handle[64], void** ptr);
+int b200moe_peer_close(void* ptr);
+
+/* Step 1: publish this rank's per-expert counts to every rank, wait for everyone's, then build the
+ * expert plan's counts / offsets / tasks and the send / return address tables. */
+int b200moe_ep_exchange_counts(const B200MoeEpArgs* args, void* cuda_stream);
+/* Step 2: copy every local route's token row straight into its expert owner's receive buffer, at its
+ * final grouped position; returns after all ranks' rows have landed (device-side barrier). */
+int b200moe_ep_send_rows(const B200MoeEpArgs* args, void* cuda_stream);
+/* Step 3 (after the expert plan's gate_up + down): copy every result row straight into the
+ * token owner's return buffer at the route's grouped position; barrier; the owner then combines. */
+int b200moe_ep_return_rows(const B200MoeEpArgs* args, void* cuda_stream);
 
 void b200moe_plan_destroy(B200MoePlan* plan);
 

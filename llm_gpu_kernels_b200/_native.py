@@ -31,7 +31,8 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_STATE = -1, -2, -3, -4
 class Shape(ctypes.Structure):
     _fields_ = [(name, ctypes.c_int32) for name in (
         "tokens", "experts", "topk", "hidden", "intermediate", "ids_are_int64", "gate_up_format",
-        "down_format", "schedule", "token_tile", "use_router", "route_only")] + [("reserved", ctypes.c_int32 * 4)]
+        "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch")] + [
+        ("reserved", ctypes.c_int32 * 3)]
 
 
 WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "ranks",
@@ -62,6 +63,18 @@ class DispatchArgs(ctypes.Structure):
 
 
 STATIC_DISPATCH_MAX_ROUTES = 65536
+EP_MAX_RANKS = 8
+
+
+class EpArgs(ctypes.Structure):
+    """``B200MoeEpArgs``: expert parallelism over peer memory."""
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "rank", "world", "experts", "topk", "hidden", "tokens", "capacity", "token_tile", "ids_are_int64")] + [
+        ("reserved", ctypes.c_int32 * 3)] + [(name, ctypes.c_void_p) for name in (
+            "x", "ids", "ranks", "counts", "expert_counts", "expert_offsets", "expert_tasks", "expert_rows",
+            "expert_output", "tables", "status")] + [(name, ctypes.c_void_p * EP_MAX_RANKS) for name in (
+                "recv_rows_peers", "return_rows_peers", "all_counts_peers", "flags_peers")]
+
 
 EXPORTS = {
     "b200moe_abi_version": (ctypes.c_int, []),
@@ -76,6 +89,15 @@ EXPORTS = {
     "b200moe_down": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_dispatch_static": (ctypes.c_int, [ctypes.POINTER(DispatchArgs), ctypes.c_void_p]),
+    "b200moe_ep_table_ints": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32]),
+    "b200moe_peer_alloc": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]),
+    "b200moe_peer_free": (ctypes.c_int, [ctypes.c_void_p]),
+    "b200moe_peer_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "b200moe_peer_import": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "b200moe_peer_close": (ctypes.c_int, [ctypes.c_void_p]),
+    "b200moe_ep_exchange_counts": (ctypes.c_int, [ctypes.POINTER(EpArgs), ctypes.c_void_p]),
+    "b200moe_ep_send_rows": (ctypes.c_int, [ctypes.POINTER(EpArgs), ctypes.c_void_p]),
+    "b200moe_ep_return_rows": (ctypes.c_int, [ctypes.POINTER(EpArgs), ctypes.c_void_p]),
     "b200moe_plan_destroy": (None, [ctypes.c_void_p]),
 }
 

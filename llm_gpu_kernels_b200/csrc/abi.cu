@@ -231,6 +231,8 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.token_tile = tile;
   w.schedule = schedule;
   w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + (s.route_only ? 0 : 3);
+  if (s.route_only == 2) w.launches -= 1;            // no row copy
+  if (s.external_dispatch) w.launches = s.tokens == 0 ? 0 : 2;  // gate_up + down only
   *out = p;
   return B200MOE_OK;
 }
@@ -263,27 +265,33 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     return B200MOE_ERR_UNSUPPORTED;
   }
   if (s.tokens > 0) {
-    struct Named { const void* ptr; const char* name; };
     if (!s.route_only && (!b->gate_up || !b->down || !b->activated)) {
       set_error("gate_up, down and activated buffers are required unless the plan is route_only");
       return B200MOE_ERR_INVALID;
     }
-    const Named needed[] = {{b->x, "x"}, {b->ids, "ids"},
-                            {b->routing_weights, "routing_weights"}, {b->output, "output"}, {b->counts, "counts"},
-                            {b->offsets, "offsets"}, {b->cursors, "cursors"}, {b->tasks, "tasks"},
-                            {b->mapping, "mapping"}, {b->ranks, "ranks"}, {b->grouped_input, "grouped_input"},
-                            {b->down_output, "down_output"}, {b->status, "status"},
-                            {b->scratch, "scratch"}};
-    for (const Named& n : needed) {
+    struct Named { const void* ptr; const char* name; };
+    const Named always[] = {{b->counts, "counts"}, {b->offsets, "offsets"}, {b->tasks, "tasks"},
+                            {b->down_output, "down_output"}, {b->status, "status"}};
+    const Named own_dispatch[] = {{b->x, "x"}, {b->ids, "ids"}, {b->routing_weights, "routing_weights"},
+                                  {b->output, "output"}, {b->cursors, "cursors"}, {b->mapping, "mapping"},
+                                  {b->ranks, "ranks"}, {b->scratch, "scratch"}};
+    auto check = [](const Named& n) {
       if (!n.ptr) {
         set_error("buffer '%s' is null", n.name);
-        return B200MOE_ERR_INVALID;
+        return false;
       }
       if (reinterpret_cast<uintptr_t>(n.ptr) % 4) {
         set_error("buffer '%s' is not 4-byte aligned", n.name);
-        return B200MOE_ERR_INVALID;
+        return false;
       }
-    }
+      return true;
+    };
+    for (const Named& n : always)
+      if (!check(n)) return B200MOE_ERR_INVALID;
+    if (!s.external_dispatch)
+      for (const Named& n : own_dispatch)
+        if (!check(n)) return B200MOE_ERR_INVALID;
+    if (s.route_only != 2 && !check({b->grouped_input, "grouped_input"})) return B200MOE_ERR_INVALID;
     if (s.use_router && !b->router_weight) {
       set_error("use_router is set but router_weight is null");
       return B200MOE_ERR_INVALID;
@@ -361,6 +369,10 @@ int b200moe_dispatch(B200MoePlan* p, void* stream) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
+  if (p->shape.external_dispatch) {
+    set_error("an external_dispatch plan receives grouped rows and metadata from outside");
+    return B200MOE_ERR_STATE;
+  }
   return check_cuda(launch_dispatch(*p, static_cast<cudaStream_t>(stream)), "dispatch launch");
 }
 
@@ -395,11 +407,19 @@ int b200moe_combine(B200MoePlan* p, void* stream) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
+  if (p->shape.external_dispatch) {
+    set_error("an external_dispatch plan has no combine stage");
+    return B200MOE_ERR_STATE;
+  }
   return check_cuda(launch_combine(*p, static_cast<cudaStream_t>(stream)), "combine launch");
 }
 
 int b200moe_forward(B200MoePlan* p, void* stream) {
   int rc;
+  if (p && p->bound && p->shape.external_dispatch) {
+    if ((rc = b200moe_gate_up(p, stream))) return rc;
+    return b200moe_down(p, stream);
+  }
   if ((rc = b200moe_router(p, stream))) return rc;
   if ((rc = b200moe_dispatch(p, stream))) return rc;
   if (p && p->shape.route_only) return B200MOE_OK;  // experts run elsewhere; the caller combines later

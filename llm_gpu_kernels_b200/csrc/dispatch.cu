@@ -265,7 +265,7 @@ dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restri
     mapping[q] = pos;
   }
   pos = __shfl_sync(0xffffffffu, pos, 0);
-  if (!valid) return;
+  if (!valid || grouped == nullptr) return;
   const __nv_bfloat16* src = x + static_cast<size_t>(q / K) * H;
   __nv_bfloat16* dst = grouped + static_cast<size_t>(pos) * H;
   if ((H & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grouped)) & 15) == 0) {
@@ -305,9 +305,10 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
                                                     offsets, cursors, tasks, status, router_flag, valid, R, E,
                                                     p.warp_routes, p.token_tile);
     }
-    dispatch_copy_kernel<<<(R + kWarps - 1) / kWarps, kThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(p.buf.x), mapping, static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
-        sh.hidden, sh.topk);
+    if (sh.route_only != 2)  // 2: the rows are sent straight to their expert owners instead
+      dispatch_copy_kernel<<<(R + kWarps - 1) / kWarps, kThreads, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(p.buf.x), mapping, static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
+          sh.hidden, sh.topk);
     return cudaPeekAtLastError();
   }
   if (sh.ids_are_int64) {
@@ -323,7 +324,7 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
       hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile);
   const int pblocks = (R + kWarps - 1) / kWarps;
   auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
-  auto* grouped = static_cast<__nv_bfloat16*>(p.buf.grouped_input);
+  auto* grouped = sh.route_only == 2 ? nullptr : static_cast<__nv_bfloat16*>(p.buf.grouped_input);
   if (sh.ids_are_int64) {
     dispatch_permute_kernel<long long><<<pblocks, kThreads, 0, s>>>(
         x, static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,

@@ -105,7 +105,7 @@ class PreparedMoE:
                              "(1=IDs, 2=nonfinite weights, 4=kernel wait timeout)")
 
     def _stage(self, index):
-        if self.x.shape[0]:
+        if self.launches:
             self.launches[index].run()
 
     def route(self):
@@ -207,7 +207,7 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
-             route_only_experts=None, valid_routes=None):
+             route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
@@ -229,7 +229,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
                           use_router=int(router_weight is not None),
-                          route_only=int(route_only_experts is not None))
+                          route_only=0 if route_only_experts is None else (1 if copy_rows else 2))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -250,6 +250,10 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
             kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
             valid_routes=valid_routes)
+        for name, tensor in (workspace or {}).items():  # caller-provided workspace (peer-visible buffers)
+            if tuple(tensor.shape) != tuple(getattr(plan, name).shape) or tensor.dtype != getattr(plan, name).dtype:
+                raise ValueError(f"workspace override {name} has the wrong shape or dtype")
+            setattr(plan, name, tensor)
         expected = {"output": plan.output, "counts": plan.counts, "offsets": plan.offsets,
                     "cursors": plan.cursors, "tasks": plan.tasks, "mapping": plan.mapping, "ranks": plan.ranks,
                     "grouped_input": plan.grouped_input, "activated": plan.activated,
@@ -285,3 +289,49 @@ def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, s
     """Drop-in for reference ``prepare_moe`` (moe.py:220-245)."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
                     token_tile=token_tile)
+
+
+def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None):
+    """Plan for the expert-owning side of expert parallelism: rows arrive already grouped by expert in
+    ``grouped_input`` ([capacity,H], written by other ranks) and counts / offsets / tasks are written by the
+    exchange kernels; the plan runs gate_up + down only (``launches[2]`` and ``launches[3]``)."""
+    capacity, h = grouped_input.shape
+    device = grouped_input.device
+    dummy_x = grouped_input  # only shapes are taken from it
+    ids = torch.zeros((capacity, 1), dtype=torch.int32, device=device)
+    rw = torch.ones((capacity, 1), dtype=torch.float32, device=device)
+    e, h2, intermediate = _validate(dummy_x, gate_up, down, ids, rw, None, gate_up_scales, down_scales)
+    lib = _native.load()
+    shape = _native.Shape(tokens=capacity, experts=e, topk=1, hidden=h, intermediate=intermediate,
+                          gate_up_format=_native.WEIGHTS_BF16 if gate_up_scales is None else _native.WEIGHTS_W4G128,
+                          down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
+                          schedule=_native.SCHEDULE_AUTO, token_tile=int(token_tile), external_dispatch=1)
+    handle = ctypes.c_void_p()
+    _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
+    try:
+        sizes = _native.Workspace()
+        _native.check(lib.b200moe_plan_workspace(handle, ctypes.byref(sizes)))
+        bf16 = lambda shp: torch.empty(shp, device=device, dtype=torch.bfloat16)
+        int32 = lambda shp: torch.zeros(shp, device=device, dtype=torch.int32)
+        plan = PreparedMoE(
+            None, gate_up, down, None, None, None, int32((e,)), int32((e,)), int32((e,)), int32((e + 1,)), None,
+            grouped_input, bf16((0, 2 * intermediate)), bf16((capacity, intermediate)), bf16((capacity, h)),
+            int32((1,)), GemmConfig(block_m=max(16, sizes.token_tile)),
+            schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
+            kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales)
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
+        buffers = _native.Buffers(
+            gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales), down=ptr(down), down_scales=ptr(down_scales),
+            counts=ptr(plan.counts), offsets=ptr(plan.offsets), cursors=ptr(plan.cursors), tasks=ptr(plan.tasks),
+            grouped_input=ptr(grouped_input), activated=ptr(plan.activated), down_output=ptr(plan.down_output),
+            status=ptr(plan.status))
+        with torch.cuda.device(device):
+            _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
+    except Exception:
+        lib.b200moe_plan_destroy(handle)
+        raise
+    plan._plan = handle
+    plan._forward = lib.b200moe_forward
+    calls = (lib.b200moe_router, lib.b200moe_dispatch, lib.b200moe_gate_up, lib.b200moe_down, lib.b200moe_combine)
+    plan.launches = tuple(StageLaunch(name, call, handle, device) for name, call in zip(STAGE_NAMES, calls))
+    return plan

@@ -197,3 +197,171 @@ def prepare_ep_moe(x, gate_up_local, down_local, ids, routing_weights, *, expert
                           router_weight=router_weight, capacity=capacity, global_routes=max(1, routes * world),
                           gate_up_scales=gate_up_scales, down_scales=down_scales)
     return ExpertParallelMoE(backend, experts=experts, group=group, capacity=capacity)
+
+
+# ------------------------------------------------------------------------------------------------
+# Peer-memory mode: rows cross NVLink by plain stores from the dispatch / return kernels
+# (csrc/ep.cu). No NCCL call and no host read inside run(): the whole forward is a fixed sequence
+# of kernel launches on the current stream.
+
+class _DeviceBytes:
+    """Exposes a raw device allocation to torch through the CUDA array interface."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerBuffers:
+    """One peer-visible allocation per name on every rank; ``ptrs[name][g]`` is rank g's buffer as mapped here."""
+
+    def __init__(self, sizes: dict, group=None):
+        import ctypes
+        from . import _native
+        self._native, self._ctypes = _native, ctypes
+        self.lib = _native.load()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.local, self.ptrs, self._imported = {}, {}, []
+        handles = {}
+        for name, nbytes in sizes.items():
+            ptr = ctypes.c_void_p()
+            _native.check(self.lib.b200moe_peer_alloc(max(256, int(nbytes)), ctypes.byref(ptr)))
+            self.local[name] = ptr.value
+            handle = ctypes.create_string_buffer(64)
+            if self.world > 1:
+                _native.check(self.lib.b200moe_peer_export(ptr, handle))
+            handles[name] = handle.raw
+        everyone = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(everyone, handles, group=group)
+        for name in sizes:
+            row = []
+            for g in range(self.world):
+                if g == self.rank:
+                    row.append(self.local[name])
+                else:
+                    ptr = ctypes.c_void_p()
+                    _native.check(self.lib.b200moe_peer_import(everyone[g][name], ctypes.byref(ptr)))
+                    self._imported.append(ptr.value)
+                    row.append(ptr.value)
+            self.ptrs[name] = row
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def tensor(self, name, nbytes, device):
+        return torch.as_tensor(_DeviceBytes(self.local[name], nbytes), device=device)
+
+    def close(self):
+        if self.lib is None:
+            return
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody may still be writing into a buffer about to go away
+        for ptr in self._imported:
+            self.lib.b200moe_peer_close(self._ctypes.c_void_p(ptr))
+        for ptr in self.local.values():
+            self.lib.b200moe_peer_free(self._ctypes.c_void_p(ptr))
+        self.lib = None
+
+
+class PeerExpertParallelMoE:
+    """Expert-parallel layer whose exchange runs inside the kernels over peer memory."""
+
+    def __init__(self, x, gate_up_local, down_local, ids, routing_weights, *, experts, router_weight=None,
+                 group=None, capacity=None, gate_up_scales=None, down_scales=None):
+        import ctypes
+        from . import _native
+        from .moe import _prepare_expert_side
+        self._native = _native
+        self.lib = _native.load()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > _native.EP_MAX_RANKS:
+            raise ValueError("peer-memory expert parallelism covers the GPUs of one node (at most 8 ranks)")
+        lo, hi = expert_range(self.rank, self.world, experts)
+        if gate_up_local.shape[0] != hi - lo or down_local.shape[0] != hi - lo:
+            raise ValueError(f"rank {self.rank} must hold experts [{lo},{hi})")
+        device = x.device
+        tokens, hidden = x.shape
+        topk = ids.shape[1]
+        routes = tokens * topk
+        self.capacity = capacity if capacity is not None else max(1, routes * self.world)
+        row_bytes = hidden * 2
+        sizes = {"recv": self.capacity * row_bytes, "ret": max(1, routes) * row_bytes,
+                 "counts": self.world * experts * 4, "flags": 256}
+        with torch.cuda.device(device):
+            self.buffers = PeerBuffers(sizes, group)
+        recv = self.buffers.tensor("recv", sizes["recv"], device).view(torch.bfloat16).view(self.capacity, hidden)
+        ret = self.buffers.tensor("ret", max(1, routes) * row_bytes, device).view(torch.bfloat16)[:routes * hidden]
+        ret = ret.view(routes, hidden)
+        self.token_plan = _prepare(x, None, None, ids, routing_weights, router_weight=router_weight,
+                                   route_only_experts=experts, copy_rows=False, workspace={"down_output": ret},
+                                   warm=False)
+        inter = down_local.shape[2] * (8 if down_scales is not None else 1)
+        tensor_tiles = hidden % 8 == 0 and inter % 8 == 0 and hidden >= 64 and inter >= 64
+        tile = token_tile_for(max(1, routes * self.world), experts, 1) if tensor_tiles else 0
+        self.expert_plan = _prepare_expert_side(gate_up_local, down_local, recv, token_tile=tile,
+                                                gate_up_scales=gate_up_scales, down_scales=down_scales)
+        self.expert_rows = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.tables = torch.zeros((int(self.lib.b200moe_ep_table_ints(self.world, experts)),), dtype=torch.int32,
+                                  device=device)
+        tp, ep = self.token_plan, self.expert_plan
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        args = _native.EpArgs(rank=self.rank, world=self.world, experts=experts, topk=topk, hidden=hidden,
+                              tokens=tokens, capacity=self.capacity, token_tile=ep.token_tile,
+                              ids_are_int64=int(ids.dtype == torch.int64),
+                              x=ptr(x), ids=ptr(ids), ranks=ptr(tp.ranks), counts=ptr(tp.counts),
+                              expert_counts=ptr(ep.counts), expert_offsets=ptr(ep.offsets), expert_tasks=ptr(ep.tasks),
+                              expert_rows=ptr(self.expert_rows), expert_output=ptr(ep.down_output),
+                              tables=ptr(self.tables), status=ptr(tp.status))
+        for field, name in (("recv_rows_peers", "recv"), ("return_rows_peers", "ret"),
+                            ("all_counts_peers", "counts"), ("flags_peers", "flags")):
+            array = getattr(args, field)
+            for g in range(self.world):
+                array[g] = self.buffers.ptrs[name][g]
+        self.args = args
+        self._device = device
+        self.stats = None
+        self.run()  # warm-up forward, as every prepare entry point does
+
+    def run(self):
+        check, lib, args = self._native.check, self.lib, ctypes_byref(self.args)
+        tp, ep = self.token_plan, self.expert_plan
+        stream = torch.cuda.current_stream(self._device).cuda_stream
+        tp.route()
+        tp.dispatch()
+        check(lib.b200moe_ep_exchange_counts(args, stream))
+        check(lib.b200moe_ep_send_rows(args, stream))
+        ep.launches[2].run()   # gate/up + SwiGLU over the received rows
+        ep.launches[3].run()   # down
+        check(lib.b200moe_ep_return_rows(args, stream))
+        tp.combine()
+        return tp.output
+
+    @property
+    def rows_received(self):
+        return int(self.expert_rows.item())
+
+    def check_inputs(self):
+        flags = int(self.token_plan.status.item()) | int(self.expert_plan.status.item())
+        if flags:
+            raise ValueError(f"invalid runtime MoE inputs: GPU status={flags} "
+                             "(1=IDs, 2=nonfinite weights, 4=kernel wait timeout, 8=EP capacity)")
+
+    def close(self):
+        self.buffers.close()
+
+
+def ctypes_byref(obj):
+    import ctypes
+    return ctypes.byref(obj)
+
+
+def prepare_peer_ep_moe(x, gate_up_local, down_local, ids, routing_weights, *, experts, router_weight=None,
+                        group=None, capacity=None, gate_up_scales=None, down_scales=None):
+    """Expert-parallel layer with the exchange fused into the dispatch / return kernels over NVLink
+    peer memory. Same arguments as :func:`prepare_ep_moe`. Call ``close()`` before the process group goes away."""
+    return PeerExpertParallelMoE(x, gate_up_local, down_local, ids, routing_weights, experts=experts,
+                                 router_weight=router_weight, group=group, capacity=capacity,
+                                 gate_up_scales=gate_up_scales, down_scales=down_scales)

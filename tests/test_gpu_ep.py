@@ -50,6 +50,34 @@ def _run_rank(rank, world, port, shape, result):
         dist.all_gather(gathered, ids)
         expect = torch.bincount(torch.cat(gathered).reshape(-1).long().cpu(), minlength=experts)
         assert torch.equal(total.cpu().long(), expect)
+        # peer-memory mode: the exchange runs inside the kernels over NVLink; same bits, no host read
+        from llm_gpu_kernels_b200.moe_ep import prepare_peer_ep_moe
+        ids2, rw2 = ids.clone(), rw.clone()
+        peer = prepare_peer_ep_moe(x[mine].contiguous().to(dev), gate_up[lo:hi].contiguous().to(dev),
+                                   down[lo:hi].contiguous().to(dev), ids2, rw2, experts=experts,
+                                   router_weight=wr.to(dev) if use_router else None)
+        try:
+            for _ in range(3):
+                out2 = peer.run()
+            torch.cuda.synchronize()
+            peer.check_inputs()
+            assert torch.equal(ids2, ids) and torch.equal(out2, out)
+            assert peer.rows_received == ep.stats.rows_received
+            # new routes in place (all to the last expert: one rank receives everything), then back
+            if not use_router:
+                keep = ids2.clone()
+                ids2.fill_(experts - 1)
+                out3 = peer.run()
+                torch.cuda.synchronize()
+                peer.check_inputs()
+                ref3 = O.moe_oracle(x[mine], gate_up, down, ids2.cpu(), rw2.cpu())
+                m3 = O.error_metrics(out3.float().cpu(), ref3)
+                assert m3["relative_rms"] <= 5e-3, m3
+                assert peer.rows_received == (t_local * topk * world if rank == world - 1 else 0)
+                ids2.copy_(keep)
+                assert torch.equal(peer.run(), out)
+        finally:
+            peer.close()
         result[rank] = (m["relative_rms"], ep.stats.rows_received)
     finally:
         dist.destroy_process_group()
