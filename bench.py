@@ -211,17 +211,18 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
     }
 
 
-def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world):
+def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode):
     """Expert-parallel layer: this rank owns E/world experts and `tokens` tokens; NCCL all-to-all between ranks."""
-    from llm_gpu_kernels_b200.moe_ep import expert_range, prepare_ep_moe
+    from llm_gpu_kernels_b200.moe_ep import expert_range, prepare_ep_moe, prepare_peer_ep_moe
     wr, gate_up, down = weights_cpu
     e, h, k = QWEN["experts"], QWEN["hidden"], QWEN["topk"]
     lo, hi = expert_range(rank, world, e)
     x = x_host.to(dev)
     ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
     rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
-    ep = prepare_ep_moe(x, gate_up[lo:hi].contiguous().to(dev), down[lo:hi].contiguous().to(dev), ids, rw,
-                        experts=e, router_weight=wr.to(dev))
+    prepare = prepare_ep_moe if mode == "nccl" else prepare_peer_ep_moe
+    ep = prepare(x, gate_up[lo:hi].contiguous().to(dev), down[lo:hi].contiguous().to(dev), ids, rw,
+                 experts=e, router_weight=wr.to(dev))
     stream = torch.cuda.current_stream(dev)
     for _ in range(max(3, warmup)):
         ep.run()
@@ -246,9 +247,15 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world):
     barrier()
     e2e_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
-    launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
-    return {"ms": ms, "ms_e2e": e2e_ms, "rows_received": ep.stats.rows_received, "launches": launches,
-            "token_tile": ep.backend.expert_plan.token_tile}
+    if mode == "nccl":
+        launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
+        rows, tile = ep.stats.rows_received, ep.backend.expert_plan.token_tile
+    else:  # router + dispatch meta, counts, send + barrier, gate_up, down, return + barrier, combine
+        launches = ep.token_plan.kernel_launches + 1 + 1 + 2 + 2 + 2
+        rows, tile = ep.rows_received, ep.expert_plan.token_tile
+        torch.distributed.barrier()
+        ep.close()
+    return {"ms": ms, "ms_e2e": e2e_ms, "rows_received": rows, "launches": launches, "token_tile": tile}
 
 
 def cpu_baseline(tokens, weights_cpu, x_cpu, repeats):
@@ -304,6 +311,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=1024, help="headline batch size")
     ap.add_argument("--weights", default="bf16", choices=("bf16", "w4"),
                     help="w4: gate/up and down packed W4G128 (int4 + BF16 group scales), BF16 activations")
+    ap.add_argument("--ep-mode", default="peer", choices=("peer", "nccl"),
+                    help="N>1: exchange rows by peer stores inside the kernels (default) or by NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-headline", action="store_true", help="time only --tokens (short profiling runs)")
     args = ap.parse_args()
@@ -351,7 +360,7 @@ def main():
             # weak scaling: every rank brings `--tokens` tokens of its own and owns E/world experts
             gx = torch.Generator().manual_seed(1000 + rank)
             x_rank = torch.randn(args.tokens, QWEN["hidden"], generator=gx).bfloat16()
-            ep = bench_ep(args.tokens, weights_cpu, x_rank, dev, args.steps, args.warmup, rank, world)
+            ep = bench_ep(args.tokens, weights_cpu, x_rank, dev, args.steps, args.warmup, rank, world, args.ep_mode)
         else:
             for tokens in sorted(xs):
                 results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
@@ -370,11 +379,13 @@ def main():
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"Qwen3-30B-A3B MoE layer forward, expert-parallel: {args.tokens} tokens per GPU, "
                                        f"E128 split {128 // world} experts per GPU, H2048 I768 top-8, BF16",
-                           "timing": "eager forwards (one host read of the all-to-all split sizes per step), CUDA events, "
-                                     "max over ranks",
+                           "timing": ("eager forwards, rows exchanged by NVLink peer stores inside the dispatch / return "
+                                      "kernels, no host read" if args.ep_mode == "peer" else
+                                      "eager forwards, NCCL all-to-all, one host read of the split sizes per step")
+                                     + ", CUDA events, max over ranks",
                            "l2": "inputs larger than L2: each rank streams its experts' weights "
                                  f"({1.2 / world:.2f} GB) per step",
-                           "parallelism": f"ep{world}", "token_tile": ep["token_tile"],
+                           "parallelism": f"ep{world}", "ep_mode": args.ep_mode, "token_tile": ep["token_tile"],
                            "rows_received_max": max_rows, "rows_received_mean": mean_rows},
                 "e2e": {"value": world * args.tokens / (e2e_ms * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": args.tokens * QWEN["hidden"] * 2,
