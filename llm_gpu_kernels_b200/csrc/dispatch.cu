@@ -31,6 +31,7 @@ namespace {
 constexpr int kWarps = kDispatchWarps;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxExperts = 256;
+constexpr int kFusedIters = kFusedRoutes / 1024;  // routes per lane of the one-block kernel
 
 // scratch layout: int32 hist[partitions][E], int32 flags[blocks], int32 router_flag
 template <typename IdT>
@@ -161,23 +162,32 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
   for (int e = lane; e < E; e += 32) warp_hist[warp][e] = 0;
   __syncthreads();
   const int begin = min(R, warp * warp_routes), end = min(R, begin + warp_routes);
+  const int iters = (end - begin + 31) >> 5;   // <= kFusedIters: kFusedRoutes / 32 warps / 32 lanes
   int my_flags = 0;
-  for (int base = begin; base < end; base += 32) {
-    const int q = base + lane;
-    const bool in = q < end, live = in && q < r_eff;
+  int key[kFusedIters], rk[kFusedIters];
+  // all loads first (one global latency for the whole range), then the in-order ranking
+#pragma unroll
+  for (int it = 0; it < kFusedIters; ++it) {
+    const int q = begin + it * 32 + lane;
+    const bool live = it < iters && q < end && q < r_eff;
     const long long id = live ? static_cast<long long>(ids[q]) : -1;
     const float w = live ? rw[q] : 0.0f;
     const bool valid = live && id >= 0 && id < E;
     if (live && !valid) my_flags |= B200MOE_STATUS_BAD_ID;
     if (live && !(fabsf(w) < INFINITY)) my_flags |= B200MOE_STATUS_BAD_WEIGHT;
-    const int key = valid ? static_cast<int>(id) : E;
-    const unsigned peers = __match_any_sync(0xffffffffu, key);
-    const int below = __popc(peers & ((1u << lane) - 1u));
-    const int rank = valid ? warp_hist[warp][key] + below : -1;
-    __syncwarp();
-    if (valid && below == 0) warp_hist[warp][key] += __popc(peers);
-    __syncwarp();
-    if (in) ranks[q] = rank;
+    key[it] = valid ? static_cast<int>(id) : E;  // E = "no expert"
+  }
+#pragma unroll
+  for (int it = 0; it < kFusedIters; ++it) {
+    if (it < iters) {  // warp-uniform
+      const unsigned peers = __match_any_sync(0xffffffffu, key[it]);
+      const int below = __popc(peers & ((1u << lane) - 1u));
+      const bool valid = key[it] < E;
+      rk[it] = valid ? warp_hist[warp][key[it]] + below : -1;
+      __syncwarp();
+      if (valid && below == 0) warp_hist[warp][key[it]] += __popc(peers);
+      __syncwarp();
+    }
   }
   if (my_flags) atomicOr(&s_flags, my_flags);
   __syncthreads();
@@ -207,17 +217,18 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
     *router_flag = 0;
   }
   __syncthreads();
-  for (int base = begin; base < end; base += 32) {
-    const int q = base + lane;
-    if (q >= end) continue;
-    const long long id = q < r_eff ? static_cast<long long>(ids[q]) : -1;
-    int rank = -1, pos = -1;
-    if (id >= 0 && id < E) {
-      rank = ranks[q] + warp_hist[warp][id];  // ranks[q] was written by this same thread above
-      pos = s_off[id] + rank;
+#pragma unroll
+  for (int it = 0; it < kFusedIters; ++it) {
+    const int q = begin + it * 32 + lane;
+    if (it < iters && q < end) {
+      int rank = -1, pos = -1;
+      if (key[it] < E) {
+        rank = rk[it] + warp_hist[warp][key[it]];  // + base rank of this warp's partition in the expert
+        pos = s_off[key[it]] + rank;
+      }
+      ranks[q] = rank;
+      mapping[q] = pos;
     }
-    ranks[q] = rank;
-    mapping[q] = pos;
   }
 }
 

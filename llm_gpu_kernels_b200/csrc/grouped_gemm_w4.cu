@@ -20,6 +20,8 @@
 //    and ran at a quarter of the bandwidth.
 //  * operand ring - per 64 K: the BF16 weight tile(s) written by the converters plus the
 //    activation rows written by the second TMA warp; consumed by the MMA warp.
+// Sixteen converter warps (four per scheduler) hide the shared-memory and BF16-ALU latency of
+// the dequantisation; each thread converts four (gate/up) or two (down) words per 64 K.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
@@ -32,7 +34,7 @@ namespace {
 using namespace ptx;
 using namespace tile;
 
-constexpr int kConverters = 256;                       // 8 warps (warps 6..13)
+constexpr int kConverters = 512;                       // 16 warps (warps 6..21)
 constexpr int kThreads = 192 + kConverters + 32;       // + words TMA, MMA, 4 epilogue, activation TMA warp
 constexpr int kMaxWords = 6, kMaxOperand = 4;
 constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
@@ -156,7 +158,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
         }
       }
     }
-  } else if (warp == 14) {
+  } else if (warp == 6 + kConverters / 32) {
     if (lane == 0) {
       // ---------------------------------------------------------------- TMA producer: activation rows
       const uint64_t pol_act = policy_evict_last();
@@ -197,13 +199,12 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
           if (!mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t w_addr = smem_u32(op_ring + static_cast<size_t>(q) * op_bytes);
-          const uint32_t a_addr = w_addr + kOpWeightBytes;
+          const uint32_t w_lo = umma_desc_lo(w_addr), a_lo = umma_desc_lo(w_addr + kOpWeightBytes);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16 = 32 bytes = 2 in descriptor units
             const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
-            const uint64_t bdesc = umma_desc(a_addr + k * kUmmaK * 2);
-            umma(d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, acc_flag);
-            if (kGateUp) umma(d_up, umma_desc(w_addr + kWTileBytes + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+            umma_lo(d_gate, w_lo + 2 * k, a_lo + 2 * k, idesc, acc_flag);
+            if (kGateUp) umma_lo(d_up, w_lo + (kWTileBytes >> 4) + 2 * k, a_lo + 2 * k, idesc, acc_flag);
           }
           umma_commit(&c->op_empty[q]);
           if (++q == num_operand) { q = 0; qph ^= 1u; }
@@ -236,9 +237,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   } else {
     // ------------------------------------------------------------------ converter warps (6..13)
     const int tid = threadIdx.x - 192;
-    const int row = tid & 127, half = tid >> 7;
-    // gate/up: half 0 converts the gate tile, half 1 the up tile, eight words per 64 K each;
-    // down: both halves share the one tile, four words per 64 K each.
+    const int row = tid & 127, part = tid >> 7;   // four threads per channel row
+    // gate/up: part&1 picks the gate or up tile, part>>1 the 16-byte half of the row's 32 bytes per 64 K
+    //          (four words each); down: part picks a quarter of the row's 32 bytes (two words each).
+    const int half = kGateUp ? (part & 1) : 0;
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
     int p = 0, q = 0;
     uint32_t pph = 0, qph = 0;
@@ -266,18 +268,17 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
           unsigned char* dst = op_ring + static_cast<size_t>(q) * op_bytes + row * 128;
           if (kGateUp) {
             dst += half * kWTileBytes;
-            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j) ^ (row & 7)) << 4));
-            const uint4 w1 = *reinterpret_cast<const uint4*>(words + (((2 * j + 1) ^ (row & 7)) << 4));
-            const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
-          } else {
-            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j + half) ^ (row & 7)) << 4));
+            const int ch = part >> 1;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j + ch) ^ (row & 7)) << 4));
             const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(dst + (((half * 4 + i) ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
+              *reinterpret_cast<uint4*>(dst + (((ch * 4 + i) ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
+          } else {
+            const uint2 w0 = *reinterpret_cast<const uint2*>(words + (((2 * j + (part >> 1)) ^ (row & 7)) << 4) +
+                                                             (part & 1) * 8);
+            *reinterpret_cast<uint4*>(dst + (((part * 2) ^ (row & 7)) << 4)) = dequant_word(w0.x, scale2);
+            *reinterpret_cast<uint4*>(dst + (((part * 2 + 1) ^ (row & 7)) << 4)) = dequant_word(w0.y, scale2);
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
           __syncwarp();

@@ -28,7 +28,7 @@ struct B200MoePlan {
   bool router_tc = false;
   CUtensorMap tm_x{};           // [T, H] bf16, box 64 x 128
   CUtensorMap tm_router_w{};    // [E, H] bf16, box 64 x round_up(E,16)
-  int router_smem = 0, router_stages = 0;
+  int router_smem = 0, router_stages = 0, router_ksplit = 1;  // ksplit = CTAs per cluster sharing one token tile
   int gemm_smem_gate_up = 0, gemm_stages_gate_up = 0;
   int gemm_smem_down = 0, gemm_stages_down = 0;
   // W4A16 kernels: packed-stage ring, operand-stage ring, dynamic shared memory
@@ -68,7 +68,7 @@ inline size_t router_flag_index(const B200MoePlan& p) {
 }
 
 constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
-constexpr int kFusedRoutes = 16384;  // up to here one 1024-thread block builds the dispatch metadata
+constexpr int kFusedRoutes = 8192;   // up to here one 1024-thread block builds the dispatch metadata
 constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels
 
 }  // namespace b200moe

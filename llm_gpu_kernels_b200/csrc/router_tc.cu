@@ -1,5 +1,9 @@
-// Router on the tensor cores: logits[token][expert] = x . Wr^T as one tcgen05
-// GEMM per 128-token tile (tokens on the TMEM lanes, experts on the columns). The
+// Router on the tensor cores: logits[token][expert] = x . Wr^T as a tcgen05 GEMM per
+// 128-token tile (tokens on the TMEM lanes, experts on the columns), with the K dimension
+// split over the CTAs of a thread-block cluster: each CTA multiplies its K slice and parks
+// its partial logits in shared memory; after a cluster barrier CTA c sums rows
+// [c*128/S, (c+1)*128/S) of all S partials through distributed shared memory (fixed order,
+// so the result is reproducible) and routes them. The
 // epilogue warps copy the FP32 logits from tensor memory to shared memory (reusing the
 // drained operand stages), then sixteen warps take rows in turn: the 32 lanes share one
 // row's experts, softmax by warp reductions, top-k by k rounds of warp arg-max done with
@@ -40,7 +44,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(kThreads, 1)
 router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_wr,
                  IdT* __restrict__ ids, float* __restrict__ rw, int* __restrict__ status, int T, int E, int H,
-                 int K, int e_pad, int num_stages) {
+                 int K, int e_pad, int num_stages, int ksplit) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -51,8 +55,12 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(e_pad)) tmem_cols <<= 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * kTileTokens;
+  uint32_t cta_rank;  // rank inside the cluster = K slice
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+  const int t0 = (blockIdx.x / ksplit) * kTileTokens;
   const int num_kb = (H + kBlockK - 1) / kBlockK;
+  const int kb_per = (num_kb + ksplit - 1) / ksplit;
+  const int kb0 = min(num_kb, static_cast<int>(cta_rank) * kb_per), kb1 = min(num_kb, kb0 + kb_per);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
@@ -68,13 +76,15 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
+  const int ld = e_pad + 1;                            // row stride in floats: conflict-free column writes
+  float* logits = reinterpret_cast<float*>(stages);    // [128][ld] partial logits, aliases the drained operand stages
 
   if (warp == 0) {
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();  // x is read again by dispatch, Wr by every tile
       int stage = 0, issued = 0;
       uint32_t phase = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) break;
         unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
         mbar_expect_tx(&c->full[stage], stage_bytes);
@@ -96,48 +106,56 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&c->full[stage], phase, &c->abort, status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t x_addr = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
         const uint32_t w_addr = x_addr + kXBytes;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma(tmem_base, umma_desc(x_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma(tmem_base, umma_desc(x_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb > kb0 || k != 0) ? 1u : 0u);
         umma_commit(&c->empty[stage]);
         if (++stage == num_stages) { stage = 0; phase ^= 1u; }
       }
-      umma_commit(&c->tmem_full);  // also the drain point when the loop gave up
+      if (kb1 > kb0) umma_commit(&c->tmem_full);  // also the drain point when the loop gave up
+      else mbar_arrive(&c->tmem_full);            // empty K slice: nothing to wait for
       if (!ok) mbar_wait_plain(&c->tmem_full, 0);
     }
-  } else {
-    // ---------------------------------------------------------------- epilogue: warps 2..9
-    const int ld = e_pad + 1;                       // row stride in floats: conflict-free column writes
-    float* logits = reinterpret_cast<float*>(stages);   // [128][ld], aliases the drained operand stages
-    bool ready = true;
-    if (warp < 6) {
-      const int quarter = warp & 3;                 // the TMEM lane quarter this warp may read
-      ready = __all_sync(0xffffffffu, mbar_wait(&c->tmem_full, 0, &c->abort, status));
-      if (ready) {
-        tc_fence_after();
-        const int r = quarter * 32 + lane;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        for (int c0 = 0; c0 < e_pad; c0 += 16) {
-          uint32_t v[16];
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- TMEM -> shared memory (this CTA's partial)
+    const int quarter = warp & 3;                 // the TMEM lane quarter this warp may read
+    const bool ready = __all_sync(0xffffffffu, mbar_wait(&c->tmem_full, 0, &c->abort, status));
+    if (ready) {
+      tc_fence_after();
+      const int r = quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      for (int c0 = 0; c0 < e_pad; c0 += 16) {
+        uint32_t v[16];
+        if (kb1 > kb0) {
           tmem_ld16(taddr + c0, v);
           tmem_ld_wait();
+        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) logits[r * ld + c0 + j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) v[j] = 0u;  // empty K slice contributes zero
         }
-      } else {
-        c->abort = 1;  // tell the row workers not to touch the logits
+#pragma unroll
+        for (int j = 0; j < 16; ++j) logits[r * ld + c0 + j] = __uint_as_float(v[j]);
       }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kRowWarps * 32) : "memory");  // TMEM readers -> row workers
-    if (*reinterpret_cast<volatile int*>(&c->abort) == 0) {
-      const int rows_live = min(kTileTokens, T - t0);
-      const int per_lane = e_pad / 32 + ((e_pad % 32) ? 1 : 0);   // <= 8 experts per lane
-      for (int r = warp - 2; r < rows_live; r += kRowWarps) {
+  }
+  // every CTA's partial is in its shared memory
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp >= 2) {
+    // ---------------------------------------------------------------- rows of this CTA: reduce over the cluster, route
+    const int rows_live = min(kTileTokens, T - t0);
+    const int rows_per_cta = kTileTokens / ksplit;
+    const int per_lane = e_pad / 32 + ((e_pad % 32) ? 1 : 0);   // <= 8 experts per lane
+    const uint32_t logits_addr = smem_u32(logits);
+    for (int rr = warp - 2; rr < rows_per_cta; rr += kRowWarps) {
+      const int r = static_cast<int>(cta_rank) * rows_per_cta + rr;
+      if (r >= rows_live) break;
+      {
         // key(x): unsigned, monotonic in x; 0 is below every finite logit and marks "absent / taken"
         uint32_t key[8];
         uint32_t kmax_local = 0;
@@ -146,7 +164,16 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           const int e = j * 32 + lane;
           uint32_t u = 0;
           if (j < per_lane && e < E) {
-            u = __float_as_uint(logits[r * ld + e]);
+            float sum_parts = 0.0f;
+            for (int sidx = 0; sidx < ksplit; ++sidx) {  // fixed order: slice 0, 1, ...
+              uint32_t remote;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                           : "=r"(remote) : "r"(logits_addr + static_cast<uint32_t>((r * ld + e) * 4)), "r"(sidx));
+              float part;
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
+              sum_parts += part;
+            }
+            u = __float_as_uint(sum_parts);
             u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;
           }
           key[j] = u;
@@ -197,6 +224,9 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
   }
 
+  // no CTA may leave while another still reads its partial
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -208,13 +238,26 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
 }  // namespace
 
+int router_ksplit(int hidden) {
+  const int num_kb = (hidden + kBlockK - 1) / kBlockK;
+  int split = 1;
+  while (split < 8 && num_kb / (split * 2) >= 2) split *= 2;  // at least two k-blocks per CTA
+  return split;
+}
+
 int configure_router_tc(B200MoePlan& p) {
   const int e_pad = (p.shape.experts + 15) / 16 * 16;
   const int stage = kTileTokens * 128 + e_pad * 128;
+  const int num_kb = (p.shape.hidden + kBlockK - 1) / kBlockK;
+  const int ksplit = router_ksplit(p.shape.hidden);
+  const int kb_per = (num_kb + ksplit - 1) / ksplit;
   int stages = (kSmemLimit - kCtrlBytes - 1024) / stage;
   if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
+  while (stages * stage < kTileTokens * (e_pad + 1) * 4) ++stages;  // the partial logits reuse this space
   p.router_stages = stages;
   p.router_smem = kCtrlBytes + 1024 + stages * stage;
+  p.router_ksplit = ksplit;
   cudaError_t e = cudaFuncSetAttribute(router_tc_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(router_tc_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
@@ -225,22 +268,34 @@ int configure_router_tc(B200MoePlan& p) {
   return B200MOE_OK;
 }
 
-cudaError_t launch_router_tc(const B200MoePlan& p, cudaStream_t s) {
+template <typename IdT>
+cudaError_t launch_router_typed(const B200MoePlan& p, cudaStream_t s, IdT* ids) {
   const auto& sh = p.shape;
-  const int grid = (sh.tokens + kTileTokens - 1) / kTileTokens;
+  const int tiles = (sh.tokens + kTileTokens - 1) / kTileTokens;
   const int e_pad = (sh.experts + 15) / 16 * 16;
-  auto* rw = static_cast<float*>(p.buf.routing_weights);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * p.router_ksplit);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = p.router_smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.router_ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
-  if (sh.ids_are_int64) {
-    router_tc_kernel<long long><<<grid, kThreads, p.router_smem, s>>>(
-        p.tm_x, p.tm_router_w, static_cast<long long*>(p.buf.ids), rw, status, sh.tokens, sh.experts, sh.hidden,
-        sh.topk, e_pad, p.router_stages);
-  } else {
-    router_tc_kernel<int><<<grid, kThreads, p.router_smem, s>>>(
-        p.tm_x, p.tm_router_w, static_cast<int*>(p.buf.ids), rw, status, sh.tokens, sh.experts, sh.hidden, sh.topk,
-        e_pad, p.router_stages);
-  }
-  return cudaPeekAtLastError();
+  return cudaLaunchKernelEx(&cfg, router_tc_kernel<IdT>, p.tm_x, p.tm_router_w, ids,
+                            static_cast<float*>(p.buf.routing_weights), status, sh.tokens, sh.experts, sh.hidden,
+                            sh.topk, e_pad, p.router_stages, p.router_ksplit);
+}
+
+
+cudaError_t launch_router_tc(const B200MoePlan& p, cudaStream_t s) {
+  cudaError_t e = p.shape.ids_are_int64 ? launch_router_typed<long long>(p, s, static_cast<long long*>(p.buf.ids))
+                                        : launch_router_typed<int>(p, s, static_cast<int*>(p.buf.ids));
+  return e != cudaSuccess ? e : cudaPeekAtLastError();
 }
 
 }  // namespace b200moe
