@@ -7,6 +7,7 @@
 // mapping < 0 (invalid expert id) contribute nothing (moe.py:117).
 #include <cuda_bf16.h>
 #include "plan.h"
+#include "pdl.cuh"
 
 namespace b200moe {
 namespace {
@@ -18,6 +19,8 @@ __global__ void __launch_bounds__(kThreads)
 combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict__ mapping,
                const float* __restrict__ rw, __nv_bfloat16* __restrict__ out, const int* __restrict__ valid_routes,
                int H, int K) {
+  pdl_launch_dependents();
+  pdl_wait();  // down_output / mapping come from the kernels before
   const int token = blockIdx.x;
   if (valid_routes && token * K >= *valid_routes) return;  // padding rows of a fixed-capacity buffer
   __shared__ int s_pos[32];
@@ -84,12 +87,12 @@ cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s) {
                    ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(o)) & 15) == 0;
   if (vec) {
     dim3 grid(sh.tokens, (sh.hidden / 8 + kThreads - 1) / kThreads);
-    combine_kernel<true><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
+    launch_pdl(combine_kernel<true>, grid, dim3(kThreads), 0, s, d, static_cast<const int*>(p.buf.mapping),
                                                    static_cast<const float*>(p.buf.routing_weights), o,
                                                    static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
   } else {
     dim3 grid(sh.tokens, (sh.hidden + kThreads - 1) / kThreads);
-    combine_kernel<false><<<grid, kThreads, 0, s>>>(d, static_cast<const int*>(p.buf.mapping),
+    launch_pdl(combine_kernel<false>, grid, dim3(kThreads), 0, s, d, static_cast<const int*>(p.buf.mapping),
                                                     static_cast<const float*>(p.buf.routing_weights), o,
                                                     static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
   }

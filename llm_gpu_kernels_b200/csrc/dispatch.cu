@@ -24,6 +24,7 @@
 //            copies the token's row to grouped_input[mapping[q]].
 #include <cuda_bf16.h>
 #include "plan.h"
+#include "pdl.cuh"
 
 namespace b200moe {
 namespace {
@@ -152,6 +153,8 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
                       int* __restrict__ cursors, int* __restrict__ tasks, int* __restrict__ status,
                       int* __restrict__ router_flag, const int* __restrict__ valid_routes, int R, int E,
                       int warp_routes, int token_tile) {
+  pdl_launch_dependents();
+  pdl_wait();  // ids / routing weights may come from the router kernel just before
   const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
   __shared__ int warp_hist[32][kMaxExperts];
   __shared__ int s_off[kMaxExperts];
@@ -236,6 +239,8 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
 __global__ void __launch_bounds__(kThreads)
 dispatch_copy_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ mapping,
                      __nv_bfloat16* __restrict__ grouped, int R, int H, int K) {
+  pdl_launch_dependents();
+  pdl_wait();  // mapping comes from the kernel just before
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = blockIdx.x * kWarps + warp;
   if (q >= R) return;
@@ -308,17 +313,17 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     auto* status = static_cast<int*>(p.buf.status);
     auto* mapping = static_cast<int*>(p.buf.mapping);
     if (sh.ids_are_int64) {
-      dispatch_fused_kernel<long long><<<1, 1024, 0, s>>>(static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
+      launch_pdl(dispatch_fused_kernel<long long>, dim3(1), dim3(1024), 0, s, static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
                                                           counts, offsets, cursors, tasks, status, router_flag, valid, R,
                                                           E, p.warp_routes, p.token_tile);
     } else {
-      dispatch_fused_kernel<int><<<1, 1024, 0, s>>>(static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
+      launch_pdl(dispatch_fused_kernel<int>, dim3(1), dim3(1024), 0, s, static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
                                                     offsets, cursors, tasks, status, router_flag, valid, R, E,
                                                     p.warp_routes, p.token_tile);
     }
     if (sh.route_only != 2)  // 2: the rows are sent straight to their expert owners instead
-      dispatch_copy_kernel<<<(R + kWarps - 1) / kWarps, kThreads, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(p.buf.x), mapping, static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
+      launch_pdl(dispatch_copy_kernel, dim3((R + kWarps - 1) / kWarps), dim3(kThreads), 0, s,
+          static_cast<const __nv_bfloat16*>(p.buf.x), static_cast<const int*>(mapping), static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
           sh.hidden, sh.topk);
     return cudaPeekAtLastError();
   }

@@ -31,6 +31,7 @@
 #include "plan.h"
 #include "sm100_ptx.cuh"
 #include "gemm_tile.cuh"
+#include "pdl.cuh"
 
 namespace b200moe {
 namespace {
@@ -76,7 +77,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(&c->full[s], 1);
@@ -93,6 +94,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (warp == 1) {
     tmem_alloc(&c->tmem_base, tmem_cols);
   }
+  pdl_wait();  // everything above overlapped with the previous kernel; its outputs are needed from here on
+  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -219,7 +222,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s) {
   const int stages = kGateUp ? p.gemm_stages_gate_up : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
-  grouped_gemm_tc_kernel<kGateUp><<<grid, kThreads, smem, s>>>(
+  launch_pdl(grouped_gemm_tc_kernel<kGateUp>, dim3(grid), dim3(kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),

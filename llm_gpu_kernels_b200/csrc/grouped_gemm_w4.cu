@@ -27,6 +27,7 @@
 #include "plan.h"
 #include "sm100_ptx.cuh"
 #include "gemm_tile.cuh"
+#include "pdl.cuh"
 
 namespace b200moe {
 namespace {
@@ -98,7 +99,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_words; ++s) {
       mbar_init(&c->words_full[s], 1);
@@ -117,6 +118,8 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
+  pdl_wait();  // the previous kernel's outputs are needed from here on
+  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -326,7 +329,8 @@ cudaError_t launch_w4(const B200MoePlan& p, cudaStream_t s) {
   const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
   const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
-  grouped_gemm_w4_kernel<kGateUp><<<grid, kThreads, kGateUp ? p.w4_smem_gate_up : p.w4_smem_down, s>>>(
+  launch_pdl(grouped_gemm_w4_kernel<kGateUp>, dim3(grid), dim3(kThreads),
+             static_cast<size_t>(kGateUp ? p.w4_smem_gate_up : p.w4_smem_down), s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<const __nv_bfloat16*>(kGateUp ? p.buf.gate_up_scales : p.buf.down_scales),
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),

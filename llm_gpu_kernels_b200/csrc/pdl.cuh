@@ -1,0 +1,38 @@
+// Programmatic dependent launch: the kernels of one forward are launched so that kernel k+1 may be
+// scheduled while kernel k is still draining. Every kernel launched this way (launch_pdl) signals
+// "dependents may launch" as its first action and executes pdl_wait() before it reads anything an
+// earlier kernel wrote; pdl_wait() returns once the preceding kernel has completed and its writes are
+// visible, so launch latency and the prologue (barrier set-up, TMEM allocation, descriptor fetch) overlap
+// with the predecessor's tail. Both instructions are no-ops under an ordinary launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdlib>
+#include <utility>
+
+namespace b200moe {
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = std::getenv("B200MOE_NO_PDL") == nullptr;
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+}  // namespace b200moe

@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include "plan.h"
 #include "sm100_ptx.cuh"
+#include "pdl.cuh"
 
 namespace b200moe {
 namespace {
@@ -71,7 +72,9 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     c->abort = 0;
     mbar_init_fence();
   }
+  pdl_launch_dependents();
   if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
+  pdl_wait();  // x may be written by the kernel just before; ids / weights may still be read by it
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -278,13 +281,15 @@ cudaError_t launch_router_typed(const B200MoePlan& p, cudaStream_t s, IdT* ids) 
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = p.router_smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = p.router_ksplit;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
   return cudaLaunchKernelEx(&cfg, router_tc_kernel<IdT>, p.tm_x, p.tm_router_w, ids,
                             static_cast<float*>(p.buf.routing_weights), status, sh.tokens, sh.experts, sh.hidden,
