@@ -31,6 +31,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 QWEN = dict(experts=128, hidden=2048, intermediate=768, topk=8)
+SHAPES = {"qwen": QWEN, "mixtral": dict(experts=8, hidden=4096, intermediate=14336, topk=2)}
 TOKENS = (17, 193, 1024)
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
@@ -45,6 +46,7 @@ def measured_peaks():
 
 
 def seeded_weights(seed=0, wscale=0.02, **shape):
+    shape.pop("topk", None)
     e, h, i = shape["experts"], shape["hidden"], shape["intermediate"]
     g = torch.Generator().manual_seed(seed)
     wr = (wscale * torch.randn(e, h, generator=g)).bfloat16()
@@ -123,18 +125,38 @@ def event_ms(fn, steps, stream):
     return start.elapsed_time(end) / steps
 
 
-def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=None):
+def zipf_bias(experts, s, seed=0):
+    """log pmf of a Zipf(s) popularity over a seeded random permutation of the experts."""
+    g = torch.Generator().manual_seed(seed)
+    pmf = torch.arange(1, experts + 1, dtype=torch.float64) ** (-s)
+    pmf = (pmf / pmf.sum())[torch.randperm(experts, generator=g)]
+    return pmf.log().float()
+
+
+def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=None, shape=QWEN, token_tile=0,
+                 zipf=0.0):
     """Prepare one layer at T tokens and time it: graph replay, eager, gate/up stage, end to end.
     `packed` = (PackedGateUp gate/up, PackedGateUp down) on the device selects the W4A16 path."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
     from llm_gpu_kernels_b200.moe_w4_cuda import prepare_w4_moe
     from oracle.moe_oracle import algorithmic_work
     wr, gate_up, down, x_host = weights
-    e, h, i, k = QWEN["experts"], QWEN["hidden"], QWEN["intermediate"], QWEN["topk"]
+    e, h, i, k = shape["experts"], shape["hidden"], shape["intermediate"], shape["topk"]
     x = x_host.to(dev)
     ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
     rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
-    if packed is None:
+    if zipf > 0:
+        # skewed routing: the popularity prior is added to the router logits on the host (the device router has
+        # no bias input), so this case runs the fixed-route path: dispatch + experts + combine
+        logits = x_host.float() @ wr.float().cpu().T + zipf_bias(e, zipf)
+        p = torch.softmax(logits, dim=1)
+        w_top, id_top = torch.topk(p, k, dim=-1)
+        ids.copy_(id_top.to(torch.int32))
+        rw.copy_(w_top / w_top.sum(-1, keepdim=True))
+        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, token_tile=token_tile)
+    elif packed is None and token_tile:
+        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr, token_tile=token_tile)
+    elif packed is None:
         prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr)
     else:
         prepared = prepare_w4_moe(x, packed[0], None, ids, rw, packed_down=packed[1], router_weight=wr)
@@ -204,6 +226,7 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
         "tokens": tokens, "ms_graph": graph_ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms,
         "tokens_per_s": tokens / (graph_ms * 1e-3), "tokens_per_s_e2e": tokens / (e2e_ms * 1e-3),
         "active_experts": active, "max_rows_per_expert": max_rows, "token_tile": base.token_tile,
+        "tflops": flops / (graph_ms * 1e-3) / 1e12, "tensor_frac": flops / (graph_ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
         "schedule": base.schedule, "alg_flops": flops, "alg_bytes": nbytes,
         "layer_hbm_gbs": nbytes / (graph_ms * 1e-3) / 1e9, "layer_roofline_frac": t_roof_ms / graph_ms,
         "stage_ms": stage_ms, "gate_up_alg_bytes": gate_up_bytes, "gate_up_gbs": gate_up_gbs,
@@ -233,8 +256,20 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
         torch.distributed.barrier()
         torch.cuda.synchronize(dev)
 
+    step, timing = ep.run, "eager forwards"
+    if mode == "peer":  # the whole forward is kernel launches on one stream: replay it as a CUDA graph
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=torch.cuda.Stream(device=dev)):
+            ep.run()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(dev)
+        ep.check_inputs()
+        step, timing = graph.replay, "CUDA-graph replay of one forward per step"
     barrier()
-    ms = event_ms(ep.run, steps, stream)
+    ms = event_ms(step, steps, stream)
+    barrier()
+    eager_ms = event_ms(ep.run, steps, stream)
     x_pinned = x_host.clone().pin_memory()
     out_pinned = torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory()
 
@@ -255,7 +290,8 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
         rows, tile = ep.rows_received, ep.expert_plan.token_tile
         torch.distributed.barrier()
         ep.close()
-    return {"ms": ms, "ms_e2e": e2e_ms, "rows_received": rows, "launches": launches, "token_tile": tile}
+    return {"ms": ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms, "rows_received": rows, "launches": launches,
+            "token_tile": tile, "timing": timing}
 
 
 def cpu_baseline(tokens, weights_cpu, x_cpu, repeats):
@@ -311,6 +347,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=1024, help="headline batch size")
     ap.add_argument("--weights", default="bf16", choices=("bf16", "w4"),
                     help="w4: gate/up and down packed W4G128 (int4 + BF16 group scales), BF16 activations")
+    ap.add_argument("--shape", default="qwen", choices=tuple(SHAPES), help="layer shape (qwen is the headline)")
+    ap.add_argument("--token-tile", type=int, default=0, help="rows of one expert per tile (0 = shape-only rule)")
+    ap.add_argument("--zipf", type=float, default=0.0, help="skewed routing: Zipf exponent of the expert popularity prior")
     ap.add_argument("--ep-mode", default="peer", choices=("peer", "nccl"),
                     help="N>1: exchange rows by peer stores inside the kernels (default) or by NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -334,13 +373,14 @@ def main():
         dist_ctx = True
     peaks = measured_peaks()
 
-    wr, gate_up, down, g = seeded_weights(**QWEN)
+    shape = SHAPES[args.shape]
+    wr, gate_up, down, g = seeded_weights(**{k: v for k, v in shape.items() if k != "topk"})
     weights_cpu = (wr, gate_up, down)
-    xs = {t: torch.randn(t, QWEN["hidden"], generator=g).bfloat16() for t in TOKENS}
-    if args.only_headline:
+    xs = {t: torch.randn(t, shape["hidden"], generator=g).bfloat16() for t in (TOKENS if args.shape == "qwen" else ())}
+    if args.only_headline or args.zipf > 0 or args.token_tile:
         xs = {t: v for t, v in xs.items() if t == args.tokens}
     if args.tokens not in xs:
-        xs[args.tokens] = torch.randn(args.tokens, QWEN["hidden"], generator=g).bfloat16()
+        xs[args.tokens] = torch.randn(args.tokens, shape["hidden"], generator=g).bfloat16()
     packed = None
     if args.weights == "w4":
         from llm_gpu_kernels_b200.moe_weight_quant import (dequantize_gate_up_reference, quantize_down,
@@ -364,7 +404,8 @@ def main():
         else:
             for tokens in sorted(xs):
                 results[tokens] = bench_tokens(tokens, (wr_d, gate_up_d, down_d, xs[tokens]), dev, args.steps,
-                                               args.warmup, peaks, dist_ctx, packed=packed)
+                                               args.warmup, peaks, dist_ctx, packed=packed, shape=shape,
+                                               token_tile=args.token_tile, zipf=args.zipf)
     if world > 1:
         t = torch.tensor([ep["ms"], ep["ms_e2e"], float(ep["rows_received"])], device=dev, dtype=torch.float64)
         tmax, tsum = t.clone(), t.clone()
@@ -379,10 +420,11 @@ def main():
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"Qwen3-30B-A3B MoE layer forward, expert-parallel: {args.tokens} tokens per GPU, "
                                        f"E128 split {128 // world} experts per GPU, H2048 I768 top-8, BF16",
-                           "timing": ("eager forwards, rows exchanged by NVLink peer stores inside the dispatch / return "
-                                      "kernels, no host read" if args.ep_mode == "peer" else
-                                      "eager forwards, NCCL all-to-all, one host read of the split sizes per step")
+                           "timing": ep["timing"] + (", rows exchanged by NVLink peer stores inside the dispatch / "
+                                                     "return kernels, no host read" if args.ep_mode == "peer" else
+                                                     ", NCCL all-to-all, one host read of the split sizes per step")
                                      + ", CUDA events, max over ranks",
+                           "ms_eager_rank0": ep["ms_eager"],
                            "l2": "inputs larger than L2: each rank streams its experts' weights "
                                  f"({1.2 / world:.2f} GB) per step",
                            "parallelism": f"ep{world}", "ep_mode": args.ep_mode, "token_tile": ep["token_tile"],
@@ -402,15 +444,17 @@ def main():
     ms, e2e_ms = head["ms_graph"], head["ms_e2e"]
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and args.shape == "qwen" and args.tokens <= 2048:
         cpu = cpu_baseline(args.tokens, weights_cpu, xs[args.tokens], repeats=3)
 
     line = {
         "metric": METRIC, "value": world * args.tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Qwen3-30B-A3B MoE layer forward (router+dispatch+gate/up SwiGLU+down+combine), "
-                               f"T={args.tokens} tokens per GPU, E128 H2048 I768 top-8, "
+        "config": {"workload": f"{'Qwen3-30B-A3B' if args.shape == 'qwen' else 'Mixtral-8x7B'} MoE layer forward "
+                               f"(router+dispatch+gate/up SwiGLU+down+combine), T={args.tokens} tokens per GPU, "
+                               f"E{shape['experts']} H{shape['hidden']} I{shape['intermediate']} top-{shape['topk']}, "
+                               + (f"Zipf({args.zipf}) expert popularity, fixed routes from the host router, " if args.zipf else "")
                                + ("BF16" if packed is None else "W4A16 (W4G128 gate/up and down, BF16 activations)"),
                    "timing": "CUDA-graph replay of one forward per step, CUDA events",
                    "l2": "inputs larger than L2: %s of expert weights streamed per step" % (
@@ -419,7 +463,13 @@ def main():
                    "token_tile": head["token_tile"], "schedule": head["schedule"],
                    "active_experts": head["active_experts"]},
         "roofline": {"bound": "hbm", "achieved": head["gate_up_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": head["gate_up_gbs"] / peaks["hbm_gbs"], "traffic": None,
+                     "frac": head["gate_up_gbs"] / peaks["hbm_gbs"],
+                     # dram__bytes_read + write of one gate/up launch from the ncu capture summarised in
+                     # profiles/moe_layer_subsystems_qwen_bf16.md (BF16, Qwen shape)
+                     "traffic": {17: 583.1e6, 1024: 844.1e6}.get(args.tokens) if (
+                         packed is None and args.shape == "qwen" and not args.zipf) else None,
+                     "tensor": {"achieved_tflops": head["tflops"], "peak_tflops": peaks["bf16_tflops"],
+                                "frac": head["tensor_frac"]},
                      "kernel": "grouped_gemm_tc_kernel<gate_up>" if packed is None else "grouped_gemm_w4_kernel<gate_up>", "peak_source": peaks["source"],
                      "alg_bytes_per_launch": head["gate_up_alg_bytes"],
                      "ms_per_launch": head["stage_ms"]["gate_up_swiglu"],

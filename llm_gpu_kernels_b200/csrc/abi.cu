@@ -31,8 +31,10 @@ bool tc_shape_ok(const B200MoeShape& s) {
 }
 
 int auto_token_tile(long long routes, int experts) {
-  // twice the mean rows per expert, as a power of two in [16,128]
+  // twice the mean rows per expert, as a power of two in [16,128]; 256 (one TMEM accumulator set, no
+  // epilogue overlap, but half the weight re-reads) once an expert averages 1024 rows or more
   const long long twice_mu = (2 * routes + experts - 1) / experts;
+  if (twice_mu >= 2048) return 256;
   int tile = 16;
   while (tile < 128 && tile < twice_mu) tile <<= 1;
   return tile;

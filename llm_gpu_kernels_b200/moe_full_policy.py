@@ -14,9 +14,12 @@ THRESHOLDS_MU = (8.0, 64.0)
 
 
 def token_tile_for(tokens: int, experts: int, topk: int) -> int:
-    """Twice the mean rows per expert as a power of two in [16,128] (the rule in csrc/abi.cu)."""
+    """Twice the mean rows per expert as a power of two in [16,128]; 256 from 1024 rows per expert
+    (the rule in csrc/abi.cu)."""
     routes = tokens * topk
     twice_mu = -(-2 * routes // experts)
+    if twice_mu >= 2048:
+        return 256
     tile = 16
     while tile < 128 and tile < twice_mu:
         tile <<= 1

@@ -51,7 +51,7 @@ def test_plan_create_and_workspace_sizes():
     lib.b200moe_plan_destroy(handle)
 
 
-@pytest.mark.parametrize("tokens,expect", [(17, 16), (193, 32), (1024, 128), (8192, 128)])
+@pytest.mark.parametrize("tokens,expect", [(17, 16), (193, 32), (1024, 128), (8192, 128), (16384, 256)])
 def test_token_tile_is_shape_only(tokens, expect):
     lib, code, handle = make_plan(tokens=tokens)
     ws = _native.Workspace()
