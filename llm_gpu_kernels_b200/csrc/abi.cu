@@ -354,6 +354,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->token_tile, false))) return rc;
     if ((rc = configure_tc(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && (rc = configure_w4(*p))) return rc;
+    if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && p->token_tile <= 64 && (rc = configure_w4t(*p))) return rc;
   }
   p->bound = true;
   return B200MOE_OK;
@@ -388,8 +389,11 @@ int b200moe_gate_up(B200MoePlan* p, void* stream) {
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_gate_up_generic(*p, s), "gate_up launch");
-  return check_cuda(is_w4(p->shape.gate_up_format) ? launch_gate_up_w4(*p, s) : launch_gate_up_tc(*p, s),
-                    "gate_up launch");
+  // W4: dequantised operand in tensor memory while two accumulator sets still fit beside it (tile <= 64),
+  // in shared memory above that
+  if (is_w4(p->shape.gate_up_format))
+    return check_cuda(p->token_tile <= 64 ? launch_gate_up_w4t(*p, s) : launch_gate_up_w4(*p, s), "gate_up launch");
+  return check_cuda(launch_gate_up_tc(*p, s), "gate_up launch");
 }
 
 int b200moe_down(B200MoePlan* p, void* stream) {
@@ -402,7 +406,9 @@ int b200moe_down(B200MoePlan* p, void* stream) {
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
-  return check_cuda(is_w4(p->shape.down_format) ? launch_down_w4(*p, s) : launch_down_tc(*p, s), "down launch");
+  if (is_w4(p->shape.down_format))
+    return check_cuda(p->token_tile <= 64 ? launch_down_w4t(*p, s) : launch_down_w4(*p, s), "down launch");
+  return check_cuda(launch_down_tc(*p, s), "down launch");
 }
 
 int b200moe_combine(B200MoePlan* p, void* stream) {

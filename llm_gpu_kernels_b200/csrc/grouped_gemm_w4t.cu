@@ -1,0 +1,374 @@
+// W4A16 ragged grouped GEMM: packed int4 weights (the reference's W4G128 v1
+// format) are TMA-loaded to shared memory as stored, dequantised to BF16 by
+// converter warps straight into the 128-byte-swizzled operand tile, and
+// multiplied on tcgen05 with the accumulators in tensor memory.
+//
+// Format contract (reference moe_weight_quant.py:1-6,35-52 and the device decode
+// of cuda_w4_gate_up.cu:28-41): words[e][n][kw] holds K = 8*kw .. 8*kw+7, nibble j
+// at bits [4j,4j+4), nibble = q + 8 with q in [-7,7]; one BF16 scale per
+// (expert, output channel, 128 consecutive K); the operand fed to the MMA is
+// exactly bf16_rn(float(q) * float(scale)). Here: (w >> 4j) & 0x000F000F | 0x43004300
+// gives the BF16 pair {128 + n_j, 128 + n_(j+4)}, minus 136 is the exact integer
+// q, and one BF16 multiply by the scale rounds once - the same value.
+// The reference quantises gate/up only; the same format with K = I serves down.
+//
+// This file: the dequantised weight tile never touches shared memory. The converter warps write it
+// with tcgen05.st into tensor memory (channel on the lane, 64 K = 32 packed columns per tile) and the MMA
+// takes its A operand from there; shared memory only carries the packed words (TMA, 128-byte rows) and the
+// activation rows. That removes the 32 KB store + 36 KB operand fetch per 64 K that made the
+// shared-memory-operand variant (grouped_gemm_w4.cu, used from token tile 128 up, where the accumulators
+// leave no room for two sets plus operand stages in tensor memory) heavy on shared-memory bandwidth. Converter warp w may only touch TMEM lanes 32*(w%4)..+31, so the four warps of a lane
+// quarter split the work of those 32 channels: gate/up tile x half of the 64 K (gate/up), or a quarter of
+// the 64 K each (down).
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include "plan.h"
+#include "sm100_ptx.cuh"
+#include "gemm_tile.cuh"
+#include "pdl.cuh"
+
+namespace b200moe {
+namespace {
+
+using namespace ptx;
+using namespace tile;
+
+constexpr int kConverters = 512;                       // 16 warps (warps 6..21)
+constexpr int kThreads = 192 + kConverters + 32;       // + words TMA, MMA, 4 epilogue, activation TMA warp
+constexpr int kMaxWords = 6, kMaxOperand = 4;
+constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
+constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
+constexpr uint32_t kWordsTileBytes = kTileM * kWordsK / 2;  // one packed tile of 256 K: 16 KB
+constexpr int kCtrlBytes = 4096;
+
+struct Ctrl {
+  uint64_t words_full[kMaxWords];
+  uint64_t words_empty[kMaxWords];
+  uint64_t op_full[kMaxOperand];
+  uint64_t op_empty[kMaxOperand];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+  Tables tables;
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+// Eight nibbles of one word -> eight BF16 in K order, scaled: one 16-byte chunk of the operand row.
+__device__ __forceinline__ uint4 dequant_word_t(uint32_t w, __nv_bfloat162 scale2) {
+  const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
+  uint32_t pair[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + n_j, 128 + n_(j+4)}
+    __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
+    q = __hmul2(q, scale2);
+    pair[j] = *reinterpret_cast<uint32_t*>(&q);
+  }
+  uint4 out;
+  out.x = __byte_perm(pair[0], pair[1], 0x5410);  // k0 k1
+  out.y = __byte_perm(pair[2], pair[3], 0x5410);  // k2 k3
+  out.z = __byte_perm(pair[0], pair[1], 0x7632);  // k4 k5
+  out.w = __byte_perm(pair[2], pair[3], 0x7632);  // k6 k7
+  return out;
+}
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __grid_constant__ CUtensorMap tm_act,
+                       const __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
+                       const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
+                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t ring_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
+  constexpr uint32_t kOpWeightBytes = 0;  // the weight operand lives in tensor memory
+  constexpr int kACols = kGateUp ? 64 : 32;   // TMEM columns of one operand stage: 64 K packed = 32 columns per tile
+  constexpr uint32_t kWordsBytes = kGateUp ? 2 * kWordsTileBytes : kWordsTileBytes;  // words stage
+  const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
+  const uint32_t op_bytes = kOpWeightBytes + act_bytes;                               // operand stage
+  unsigned char* op_ring = smem_raw + ring_off;
+  unsigned char* words_ring = op_ring + static_cast<size_t>(num_operand) * op_bytes;
+  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int num_acc = (2 * acc_cols + num_operand * kACols <= 512) ? 2 : 1;
+  const uint32_t a_col0 = static_cast<uint32_t>(num_acc * acc_cols);       // operand stages follow the accumulators
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < a_col0 + static_cast<uint32_t>(num_operand * kACols)) tmem_cols <<= 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < num_words; ++s) {
+      mbar_init(&c->words_full[s], 1);
+      mbar_init(&c->words_empty[s], kConverters / 32);   // one arrival per converter warp
+    }
+    for (int s = 0; s < num_operand; ++s) {
+      mbar_init(&c->op_full[s], kConverters / 32 + 1);   // converter warps + the activation TMA
+      mbar_init(&c->op_empty[s], 1);                     // the MMA commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
+    }
+    mbar_init(&c->drain, 1);
+    c->abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
+  pdl_wait();  // the previous kernel's outputs are needed from here on
+  load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
+
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const int num_kb = k_dim / kBlockK;                       // K is a multiple of 128
+  const int num_ws = (k_dim + kWordsK - 1) / kWordsK;       // words stages per tile
+  const int groups = k_dim / 128;
+  const int total_items = c->tables.tasks[E] * n_ct;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer: packed words
+      const uint64_t pol_w = stream_weights ? policy_evict_first() : policy_evict_last();
+      int p = 0;
+      uint32_t pph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
+        for (int ws = 0; ws < num_ws; ++ws) {
+          if (!mbar_wait(&c->words_empty[p], pph ^ 1u, &c->abort, status)) { ok = false; break; }
+          unsigned char* st = words_ring + static_cast<size_t>(p) * kWordsBytes;
+          mbar_expect_tx(&c->words_full[p], kWordsBytes);
+          tma_load_2d(st, &tm_words, &c->words_full[p], ws * (kWordsK / 8), w_row, pol_w);  // 32 int32 per row
+          if (kGateUp)
+            tma_load_2d(st + kWordsTileBytes, &tm_words, &c->words_full[p], ws * (kWordsK / 8), w_row + n_out, pol_w);
+          ++issued;
+          if (++p == num_words) { p = 0; pph ^= 1u; }
+        }
+      }
+      const long long first = issued > num_words ? issued - num_words : 0;
+      for (long long i = first; i < issued; ++i) {  // never leave with copies in flight
+        if (!mbar_wait_plain(&c->words_full[i % num_words], static_cast<uint32_t>((i / num_words) & 1))) {
+          atomicOr(status, B200MOE_STATUS_TIMEOUT);
+          break;
+        }
+      }
+    }
+  } else if (warp == 6 + kConverters / 32) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer: activation rows
+      const uint64_t pol_act = policy_evict_last();
+      int q = 0;
+      uint32_t qph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
+          mbar_expect_tx(&c->op_full[q], act_bytes);
+          tma_load_2d(op_ring + static_cast<size_t>(q) * op_bytes + kOpWeightBytes, &tm_act, &c->op_full[q],
+                      kb * kBlockK, t.row0, pol_act);
+          ++issued;
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
+        }
+      }
+      const long long first = issued > num_operand ? issued - num_operand : 0;
+      for (long long i = first; i < issued; ++i) {  // completes once the converters arrived too; bounded
+        if (!mbar_wait_plain(&c->op_full[i % num_operand], static_cast<uint32_t>((i / num_operand) & 1))) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      int q = 0, acc = 0;
+      uint32_t qph = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
+        if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
+        const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = umma_desc_lo(smem_u32(op_ring + static_cast<size_t>(q) * op_bytes));  // activation rows
+          const uint32_t w_tmem = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols);                 // weight tile(s)
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16: 8 TMEM columns / 2 descriptor units
+            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
+            umma_tmem_a(d_gate, w_tmem + 8 * k, a_lo + 2 * k, idesc, acc_flag);
+            if (kGateUp) umma_tmem_a(d_up, w_tmem + 32 + 8 * k, a_lo + 2 * k, idesc, acc_flag);
+          }
+          umma_commit(&c->op_empty[q]);
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&c->tmem_full[acc]);
+        if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) {
+        umma_commit(&c->drain);
+        mbar_wait_plain(&c->drain, 0);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
+      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
+      if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ converter warps (6..13)
+    const int quarter = warp & 3;                 // the TMEM lane quarter this warp may write
+    const int row = quarter * 32 + lane;          // channel row of the tile = TMEM lane
+    const int part = (warp - 6) >> 2;             // 0..3: which share of the row's 64 K this warp converts
+    // gate/up: part&1 picks the gate or up tile, part>>1 the 16-byte half of the row's 32 packed bytes;
+    // down: part picks a quarter (two words) of the row's 32 packed bytes.
+    const int half = kGateUp ? (part & 1) : 0;
+    const int tid = threadIdx.x - 192;
+    const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
+    int p = 0, q = 0;
+    uint32_t pph = 0, qph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+      long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row +
+                       (kGateUp ? half * n_out : 0);
+      if (srow >= total_rows) srow = total_rows - 1;  // lanes past the last channel are never stored
+      const __nv_bfloat16* srow_ptr = scales + srow * groups;
+      __nv_bfloat16 s0 = srow_ptr[0], s1 = srow_ptr[groups > 1 ? 1 : 0];   // the two groups of words stage 0
+      for (int ws = 0; ok && ws < num_ws; ++ws) {
+        const __nv_bfloat162 scale_lo = __bfloat162bfloat162(s0), scale_hi = __bfloat162bfloat162(s1);
+        if (ws + 1 < num_ws) {  // prefetch the next stage's scales while this one is converted
+          s0 = srow_ptr[2 * ws + 2];
+          s1 = srow_ptr[min(2 * ws + 3, groups - 1)];
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(&c->words_full[p], pph, &c->abort, status))) { ok = false; break; }
+        const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes +
+                                     (kGateUp ? half * kWordsTileBytes : 0) + row * 128;
+        const int subs = min(kWordsK, k_dim - ws * kWordsK) / kBlockK;
+        for (int j = 0; j < subs; ++j) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status))) { ok = false; break; }
+          const __nv_bfloat162 scale2 = j < 2 ? scale_lo : scale_hi;
+          tc_fence_after();  // the MMAs that read this stage last have completed (op_empty)
+          const uint32_t dst = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols) +
+                               (static_cast<uint32_t>(quarter * 32) << 16);
+          if (kGateUp) {
+            const int ch = part >> 1;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j + ch) ^ (row & 7)) << 4));
+            const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
+            uint32_t r[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 d = dequant_word_t(w[i], scale2);
+              r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
+            }
+            tmem_st16(dst + half * 32 + ch * 16, r);   // 4 words = 32 K = 16 packed columns
+          } else {
+            const uint2 w0 = *reinterpret_cast<const uint2*>(words + (((2 * j + (part >> 1)) ^ (row & 7)) << 4) +
+                                                             (part & 1) * 8);
+            const uint4 d0 = dequant_word_t(w0.x, scale2), d1 = dequant_word_t(w0.y, scale2);
+            const uint32_t r[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+            tmem_st8(dst + part * 8, r);               // 2 words = 16 K = 8 packed columns
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp
+          if (++q == num_operand) { q = 0; qph ^= 1u; }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c->words_empty[p]);
+        if (++p == num_words) { p = 0; pph ^= 1u; }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+void rings_for_t(bool gate_up, int token_tile, int* num_words, int* num_operand, int* smem_bytes) {
+  const int act = token_tile * 128;
+  const int words = (gate_up ? 2 : 1) * static_cast<int>(kWordsTileBytes);
+  const int a_cols = gate_up ? 64 : 32, acc_cols = (gate_up ? 2 : 1) * token_tile;
+  int q = kMaxOperand;                                   // operand stages live in TMEM next to the accumulators
+  while (q > 2 && acc_cols + q * a_cols > 512) --q;
+  const int budget = kSmemLimit - kCtrlBytes - 1024 - q * act;
+  int p = budget / words;
+  if (p > kMaxWords) p = kMaxWords;
+  *num_words = p;
+  *num_operand = q;
+  *smem_bytes = kCtrlBytes + 1024 + q * act + p * words;
+}
+
+template <bool kGateUp>
+cudaError_t launch_w4t(const B200MoePlan& p, cudaStream_t s) {
+  const auto& sh = p.shape;
+  const int n_out = kGateUp ? sh.intermediate : sh.hidden;
+  const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
+  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
+  const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
+  const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
+  launch_pdl(grouped_gemm_w4t_kernel<kGateUp>, dim3(grid), dim3(kThreads),
+             static_cast<size_t>(kGateUp ? p.w4t_smem_gate_up : p.w4t_smem_down), s,
+      kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
+      static_cast<const __nv_bfloat16*>(kGateUp ? p.buf.gate_up_scales : p.buf.down_scales),
+      static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
+      static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
+      static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
+      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, kGateUp ? p.w4t_packed_gate_up : p.w4t_packed_down,
+      kGateUp ? p.w4t_operand_gate_up : p.w4t_operand_down, stream_weights);
+  return cudaPeekAtLastError();
+}
+
+}  // namespace
+
+int configure_w4t(B200MoePlan& p) {
+  rings_for_t(true, p.token_tile, &p.w4t_packed_gate_up, &p.w4t_operand_gate_up, &p.w4t_smem_gate_up);
+  rings_for_t(false, p.token_tile, &p.w4t_packed_down, &p.w4t_operand_down, &p.w4t_smem_down);
+  if (p.w4t_packed_gate_up < 2 || p.w4t_packed_down < 2) {
+    set_error("token_tile %d leaves fewer than 2 stages of packed words", p.token_tile);
+    return B200MOE_ERR_INVALID;
+  }
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_w4t_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_gemm_w4t_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(W4 shared memory) failed: %s", cudaGetErrorString(e));
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s) { return launch_w4t<true>(p, s); }
+cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s) { return launch_w4t<false>(p, s); }
+
+}  // namespace b200moe

@@ -34,6 +34,9 @@ struct B200MoePlan {
   // W4A16 kernels: packed-stage ring, operand-stage ring, dynamic shared memory
   int w4_packed_gate_up = 0, w4_operand_gate_up = 0, w4_smem_gate_up = 0;
   int w4_packed_down = 0, w4_operand_down = 0, w4_smem_down = 0;
+  // the same for the variant that keeps the dequantised operand in tensor memory (token tile <= 128)
+  int w4t_packed_gate_up = 0, w4t_operand_gate_up = 0, w4t_smem_gate_up = 0;
+  int w4t_packed_down = 0, w4t_operand_down = 0, w4t_smem_down = 0;
 };
 
 namespace b200moe {
@@ -50,6 +53,8 @@ cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
 
 size_t router_smem_bytes(int hidden, int experts);
@@ -59,6 +64,7 @@ cudaError_t router_opt_in_smem(size_t bytes);
 int configure_tc(B200MoePlan& p);
 int configure_router_tc(B200MoePlan& p);
 int configure_w4(B200MoePlan& p);
+int configure_w4t(B200MoePlan& p);
 
 // The router raises its timeout flag in a scratch word (the dispatch folds it into the
 // status word, which it resets every forward): int32 index of that word inside `scratch`.
