@@ -145,6 +145,13 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
     x = x_host.to(dev)
     ids = torch.zeros(tokens, k, dtype=torch.int32, device=dev)
     rw = torch.zeros(tokens, k, dtype=torch.float32, device=dev)
+    def build(x_, ids_, rw_):
+        if zipf > 0:
+            return prepare_ranked_moe_launcher(x_, gate_up, down, ids_, rw_, token_tile=token_tile)
+        if packed is not None:
+            return prepare_w4_moe(x_, packed[0], None, ids_, rw_, packed_down=packed[1], router_weight=wr)
+        return prepare_ranked_moe_launcher(x_, gate_up, down, ids_, rw_, router_weight=wr, token_tile=token_tile)
+
     if zipf > 0:
         # skewed routing: the popularity prior is added to the router logits on the host (the device router has
         # no bias input), so this case runs the fixed-route path: dispatch + experts + combine
@@ -153,13 +160,7 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
         w_top, id_top = torch.topk(p, k, dim=-1)
         ids.copy_(id_top.to(torch.int32))
         rw.copy_(w_top / w_top.sum(-1, keepdim=True))
-        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, token_tile=token_tile)
-    elif packed is None and token_tile:
-        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr, token_tile=token_tile)
-    elif packed is None:
-        prepared = prepare_ranked_moe_launcher(x, gate_up, down, ids, rw, router_weight=wr)
-    else:
-        prepared = prepare_w4_moe(x, packed[0], None, ids, rw, packed_down=packed[1], router_weight=wr)
+    prepared = build(x, ids, rw)
     base = prepared.base
     stream = torch.cuda.current_stream(dev)
     for _ in range(max(3, warmup)):
@@ -213,8 +214,45 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
     for _ in range(3):
         e2e_step()
     barrier()
-    e2e_ms = event_ms(e2e_step, steps, stream)
+    e2e_serial_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
+
+    # the same with two forwards in flight: a second prepared layer (own activations and workspace, same
+    # weights) on a second stream, so one step's copies overlap the other step's kernels. Every step still
+    # copies its input from pinned host memory and its result back.
+    slots = [{"x": x, "prepared": prepared, "graph": graph, "x_pinned": x_pinned, "out_pinned": out_pinned,
+              "stream": torch.cuda.Stream(device=dev)}]
+    x2, ids2, rw2 = x.clone(), ids.clone(), rw.clone()
+    prepared2 = build(x2, ids2, rw2)
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2, stream=torch.cuda.Stream(device=dev)):
+        prepared2.run()
+    slots.append({"x": x2, "prepared": prepared2, "graph": graph2, "x_pinned": x_host.clone().pin_memory(),
+                  "out_pinned": torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory(),
+                  "stream": torch.cuda.Stream(device=dev)})
+
+    def e2e_pipelined(count):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for slot in slots:
+            slot["stream"].wait_event(start)
+        for i in range(count):
+            slot = slots[i % 2]
+            with torch.cuda.stream(slot["stream"]):
+                slot["x"].copy_(slot["x_pinned"], non_blocking=True)
+                slot["graph"].replay()
+                slot["out_pinned"].copy_(slot["prepared"].base.output, non_blocking=True)
+        for slot in slots:
+            stream.wait_stream(slot["stream"])
+        end.record(stream)
+        end.synchronize()
+        return start.elapsed_time(end) / count
+
+    e2e_pipelined(6)
+    barrier()
+    e2e_ms = e2e_pipelined(steps)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(slots[1]["out_pinned"], out_pinned), "the two pipeline slots disagree"
 
     w4 = packed is not None
     flops, nbytes = algorithmic_work(tokens, e, k, h, i, active, w4=w4)
@@ -223,7 +261,7 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, dist_ctx, packed=No
     gate_up_bytes = active * gate_up_weight_bytes + tokens * k * h * 2 + tokens * k * i * 2
     gate_up_gbs = gate_up_bytes / (stage_ms["gate_up_swiglu"] * 1e-3) / 1e9
     return {
-        "tokens": tokens, "ms_graph": graph_ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms,
+        "tokens": tokens, "ms_graph": graph_ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms, "ms_e2e_serial": e2e_serial_ms,
         "tokens_per_s": tokens / (graph_ms * 1e-3), "tokens_per_s_e2e": tokens / (e2e_ms * 1e-3),
         "active_experts": active, "max_rows_per_expert": max_rows, "token_tile": base.token_tile,
         "tflops": flops / (graph_ms * 1e-3) / 1e12, "tensor_frac": flops / (graph_ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
@@ -280,8 +318,45 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
     for _ in range(3):
         e2e_step()
     barrier()
-    e2e_ms = event_ms(e2e_step, steps, stream)
+    e2e_serial_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
+
+    # the same with two forwards in flight: a second prepared layer (own activations and workspace, same
+    # weights) on a second stream, so one step's copies overlap the other step's kernels. Every step still
+    # copies its input from pinned host memory and its result back.
+    slots = [{"x": x, "prepared": prepared, "graph": graph, "x_pinned": x_pinned, "out_pinned": out_pinned,
+              "stream": torch.cuda.Stream(device=dev)}]
+    x2, ids2, rw2 = x.clone(), ids.clone(), rw.clone()
+    prepared2 = build(x2, ids2, rw2)
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2, stream=torch.cuda.Stream(device=dev)):
+        prepared2.run()
+    slots.append({"x": x2, "prepared": prepared2, "graph": graph2, "x_pinned": x_host.clone().pin_memory(),
+                  "out_pinned": torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory(),
+                  "stream": torch.cuda.Stream(device=dev)})
+
+    def e2e_pipelined(count):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for slot in slots:
+            slot["stream"].wait_event(start)
+        for i in range(count):
+            slot = slots[i % 2]
+            with torch.cuda.stream(slot["stream"]):
+                slot["x"].copy_(slot["x_pinned"], non_blocking=True)
+                slot["graph"].replay()
+                slot["out_pinned"].copy_(slot["prepared"].base.output, non_blocking=True)
+        for slot in slots:
+            stream.wait_stream(slot["stream"])
+        end.record(stream)
+        end.synchronize()
+        return start.elapsed_time(end) / count
+
+    e2e_pipelined(6)
+    barrier()
+    e2e_ms = e2e_pipelined(steps)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(slots[1]["out_pinned"], out_pinned), "the two pipeline slots disagree"
     if mode == "nccl":
         launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
         rows, tile = ep.stats.rows_received, ep.backend.expert_plan.token_tile
@@ -477,7 +552,10 @@ def main():
                                "achieved_gbs": head["layer_hbm_gbs"], "frac": head["layer_roofline_frac"]}},
         "e2e": {"value": world * args.tokens / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": head["h2d_bytes"], "d2h_bytes_per_step": head["d2h_bytes"],
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "ms_per_step_one_in_flight": head["ms_e2e_serial"],
+                "mode": "prepared.run() captured once and replayed; two forwards in flight on two streams "
+                        "(double-buffered activations and workspace), each step copies its input from pinned host "
+                        "memory and its BF16 result back"},
         "gpu_launches": args.steps * head["launches"],
         "clocks": clocks.summary(),
         "by_tokens": {str(t): {k: v for k, v in r.items() if k not in ("tokens",)} for t, r in results.items()},
