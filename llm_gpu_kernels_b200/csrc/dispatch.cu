@@ -9,7 +9,7 @@
 // expert, which is the stable order of argsort(ids, stable=True). No global
 // atomics are used, so counts / offsets / ranks / mapping are bit-reproducible.
 //
-// Up to kFusedRoutes routes one 1024-thread block does count + scan + final
+// Up to kFusedRoutes (2048) routes one 1024-thread block does count + scan + final
 // ranks / mapping in a single launch (warp histograms stay in shared memory)
 // and a second kernel copies the rows. Above that, three kernels:
 //  count   - every warp owns `warp_routes` consecutive routes and walks them 32
@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(kThreads)
 dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
                       int* __restrict__ hist, int* __restrict__ flags, const int* __restrict__ valid_routes, int R,
                       int E, int warp_routes, int partitions) {
+  pdl_launch_dependents();
+  pdl_wait();  // ids / routing weights may come from the router kernel just before
   const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
   __shared__ int warp_hist[kWarps][kMaxExperts];
   __shared__ int block_flags;
@@ -108,6 +110,8 @@ dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int*
                      int* __restrict__ offsets, int* __restrict__ cursors, int* __restrict__ tasks,
                      int* __restrict__ status, int* __restrict__ router_flag, int E, int partitions, int blocks,
                      int token_tile) {
+  pdl_launch_dependents();
+  pdl_wait();  // partition histograms come from the count kernel
   __shared__ int s_scan[16];
   __shared__ int s_flags;
   const int e = threadIdx.x;
@@ -264,6 +268,8 @@ dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restri
                         int* __restrict__ ranks, int* __restrict__ mapping,
                         __nv_bfloat16* __restrict__ grouped, const int* __restrict__ valid_routes, int R, int E,
                         int H, int K, int warp_routes) {
+  pdl_launch_dependents();
+  pdl_wait();  // offsets and partition base ranks come from the scan kernel
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = blockIdx.x * kWarps + warp;
   if (q >= R) return;
@@ -328,13 +334,13 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     return cudaPeekAtLastError();
   }
   if (sh.ids_are_int64) {
-    dispatch_count_kernel<long long><<<blocks, kThreads, 0, s>>>(
+    launch_pdl(dispatch_count_kernel<long long>, dim3(blocks), dim3(kThreads), 0, s,
         static_cast<const long long*>(p.buf.ids), rw, ranks, hist, flags, valid, R, E, p.warp_routes, p.partitions);
   } else {
-    dispatch_count_kernel<int><<<blocks, kThreads, 0, s>>>(
+    launch_pdl(dispatch_count_kernel<int>, dim3(blocks), dim3(kThreads), 0, s,
         static_cast<const int*>(p.buf.ids), rw, ranks, hist, flags, valid, R, E, p.warp_routes, p.partitions);
   }
-  dispatch_scan_kernel<<<1, kMaxExperts, 0, s>>>(
+  launch_pdl(dispatch_scan_kernel, dim3(1), dim3(kMaxExperts), 0, s,
       hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
       static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status),
       hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile);
@@ -342,11 +348,11 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
   auto* grouped = sh.route_only == 2 ? nullptr : static_cast<__nv_bfloat16*>(p.buf.grouped_input);
   if (sh.ids_are_int64) {
-    dispatch_permute_kernel<long long><<<pblocks, kThreads, 0, s>>>(
+    launch_pdl(dispatch_permute_kernel<long long>, dim3(pblocks), dim3(kThreads), 0, s,
         x, static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
         static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
   } else {
-    dispatch_permute_kernel<int><<<pblocks, kThreads, 0, s>>>(
+    launch_pdl(dispatch_permute_kernel<int>, dim3(pblocks), dim3(kThreads), 0, s,
         x, static_cast<const int*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
         static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
   }

@@ -74,7 +74,8 @@ inline size_t router_flag_index(const B200MoePlan& p) {
 }
 
 constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
-constexpr int kFusedRoutes = 8192;   // up to here one 1024-thread block builds the dispatch metadata
+constexpr int kFusedRoutes = 2048;   // up to here one 1024-thread block builds the dispatch metadata; above, the
+                                     // ranking (a serial __match_any_sync walk per warp) is spread over many SMs
 constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels
 
 }  // namespace b200moe
