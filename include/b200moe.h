@@ -69,7 +69,9 @@ typedef struct {
   int32_t external_dispatch; /* 1: rows arrive already grouped by expert and counts / offsets / tasks are
                              written by someone else (the expert-owning side of expert parallelism):
                              forward = gate_up + down on grouped_input; x / ids / weights / output unused */
-  int32_t reserved[3];
+  int32_t router_bf16_weights; /* 1: the router rounds its renormalised weights through BF16, as the model the
+                             reference captured does (scripts/capture_qwen3_moe_layer0.py:587-588) */
+  int32_t reserved[2];
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned

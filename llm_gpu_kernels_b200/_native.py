@@ -31,8 +31,8 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_STATE = -1, -2, -3, -4
 class Shape(ctypes.Structure):
     _fields_ = [(name, ctypes.c_int32) for name in (
         "tokens", "experts", "topk", "hidden", "intermediate", "ids_are_int64", "gate_up_format",
-        "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch")] + [
-        ("reserved", ctypes.c_int32 * 3)]
+        "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch", "router_bf16_weights")] + [
+        ("reserved", ctypes.c_int32 * 2)]
 
 
 WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "ranks",

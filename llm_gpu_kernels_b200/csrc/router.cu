@@ -22,7 +22,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <typename IdT>
 __global__ void __launch_bounds__(kRouterThreads)
 router_topk_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
-                   IdT* __restrict__ ids, float* __restrict__ rw, int T, int E, int H, int K) {
+                   IdT* __restrict__ ids, float* __restrict__ rw, int T, int E, int H, int K, int bf16_weights) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);               // [kRouterTokens][H]
   float* logits = xs + static_cast<size_t>(kRouterTokens) * H;   // [kRouterTokens][E]
@@ -120,7 +120,8 @@ router_topk_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
   if (lane < K) {
     ids[static_cast<size_t>(token) * K + lane] = static_cast<IdT>(chosen_e);
-    rw[static_cast<size_t>(token) * K + lane] = chosen_w / total;
+    const float w = chosen_w / total;
+    rw[static_cast<size_t>(token) * K + lane] = bf16_weights ? __bfloat162float(__float2bfloat16_rn(w)) : w;
   }
 }
 
@@ -135,10 +136,10 @@ cudaError_t launch_router(const B200MoePlan& p, cudaStream_t s) {
   auto* rw = static_cast<float*>(p.buf.routing_weights);
   if (sh.ids_are_int64) {
     router_topk_kernel<long long><<<grid, kRouterThreads, smem, s>>>(
-        x, wr, static_cast<long long*>(p.buf.ids), rw, sh.tokens, sh.experts, sh.hidden, sh.topk);
+        x, wr, static_cast<long long*>(p.buf.ids), rw, sh.tokens, sh.experts, sh.hidden, sh.topk, sh.router_bf16_weights);
   } else {
     router_topk_kernel<int><<<grid, kRouterThreads, smem, s>>>(
-        x, wr, static_cast<int*>(p.buf.ids), rw, sh.tokens, sh.experts, sh.hidden, sh.topk);
+        x, wr, static_cast<int*>(p.buf.ids), rw, sh.tokens, sh.experts, sh.hidden, sh.topk, sh.router_bf16_weights);
   }
   return cudaPeekAtLastError();
 }

@@ -45,7 +45,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(kThreads, 1)
 router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_wr,
                  IdT* __restrict__ ids, float* __restrict__ rw, int* __restrict__ status, int T, int E, int H,
-                 int K, int e_pad, int num_stages, int ksplit) {
+                 int K, int e_pad, int num_stages, int ksplit, int bf16_weights) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -221,7 +221,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (lane < K) {
           const size_t o = static_cast<size_t>(t0 + r) * K + lane;
           ids[o] = static_cast<IdT>(my_e);
-          rw[o] = p / total;
+          const float w = p / total;
+          rw[o] = bf16_weights ? __bfloat162float(__float2bfloat16_rn(w)) : w;
         }
       }
     }
@@ -293,7 +294,7 @@ cudaError_t launch_router_typed(const B200MoePlan& p, cudaStream_t s, IdT* ids) 
   int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
   return cudaLaunchKernelEx(&cfg, router_tc_kernel<IdT>, p.tm_x, p.tm_router_w, ids,
                             static_cast<float*>(p.buf.routing_weights), status, sh.tokens, sh.experts, sh.hidden,
-                            sh.topk, e_pad, p.router_stages, p.router_ksplit);
+                            sh.topk, e_pad, p.router_stages, p.router_ksplit, sh.router_bf16_weights);
 }
 
 

@@ -207,7 +207,8 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
-             route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None):
+             route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None,
+             router_bf16_weights=False):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
@@ -229,7 +230,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
                           use_router=int(router_weight is not None),
-                          route_only=0 if route_only_experts is None else (1 if copy_rows else 2))
+                          route_only=0 if route_only_experts is None else (1 if copy_rows else 2),
+                          router_bf16_weights=int(bool(router_bf16_weights)))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -285,10 +287,12 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
     return plan
 
 
-def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0):
-    """Drop-in for reference ``prepare_moe`` (moe.py:220-245)."""
+def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0,
+                router_bf16_weights=False):
+    """Drop-in for reference ``prepare_moe`` (moe.py:220-245). ``router_bf16_weights`` makes the router round
+    its weights through BF16 like the captured model does (scripts/capture_qwen3_moe_layer0.py:587-588)."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
-                    token_tile=token_tile)
+                    token_tile=token_tile, router_bf16_weights=router_bf16_weights)
 
 
 def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None):

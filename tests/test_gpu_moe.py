@@ -174,6 +174,26 @@ def test_large_route_count_multi_block_dispatch(dev, pattern):
     check_output(out, cpu)
 
 
+@pytest.mark.parametrize("schedule", [None, "generic"])
+def test_router_bf16_rounded_weights(dev, schedule):
+    """The captured model's convention: weights rounded through BF16, then promoted (capture script :587-588)."""
+    from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    wr, gate_up, down, x = seeded_layer(8, 70, 256, 128, 16, wscale=0.05)
+    ids = torch.zeros(70, 4, dtype=torch.int32, device=dev)
+    rw = torch.zeros(70, 4, dtype=torch.float32, device=dev)
+    p = prepare_ranked_moe_launcher(x.to(dev), gate_up.to(dev), down.to(dev), ids, rw, router_weight=wr.to(dev),
+                                    schedule=schedule, router_bf16_weights=True)
+    out = p.run()
+    torch.cuda.synchronize()
+    got = rw.cpu()
+    assert torch.equal(got.bfloat16().float(), got)                 # exact promotions of BF16 values
+    ref_ids, ref_w, _ = O.router_oracle(x, wr, 4, bf16_weights=True)
+    same = ids.cpu() == ref_ids
+    assert same.float().mean() > 0.99
+    assert (got[same] - ref_w[same]).abs().max() <= 2.0 ** -8       # at most one BF16 step apart
+    check_output(out, (x, gate_up, down, ids.cpu(), got))
+
+
 def test_tiny_layer_golden(dev, golden_dir):
     """BASELINE config 1 against the reference's own output on the same seeded inputs."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
