@@ -2,6 +2,7 @@
 // descriptor encoding, and the launch sequence. See include/b200moe.h.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include "plan.h"
@@ -215,6 +216,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
     p->partitions = static_cast<int>((r + p->warp_routes - 1) / p->warp_routes);
   }
   const int blocks = (p->partitions + kDispatchWarps - 1) / kDispatchWarps;
+  p->chain_words = 1 + s.experts;
 
   B200MoeWorkspace& w = p->ws;
   const size_t T = s.tokens, H = s.hidden, I = s.intermediate, E = s.experts, R = r;
@@ -229,7 +231,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.activated = s.route_only ? 0 : R * I * 2;
   w.down_output = R * H * 2;
   w.status = 4;
-  w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 1) * 4);
+  w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 2 + E) * 4);
   w.token_tile = tile;
   w.schedule = schedule;
   w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + (s.route_only ? 0 : 3);
@@ -379,7 +381,20 @@ int b200moe_dispatch(B200MoePlan* p, void* stream) {
   return check_cuda(launch_dispatch(*p, static_cast<cudaStream_t>(stream)), "dispatch launch");
 }
 
-int b200moe_gate_up(B200MoePlan* p, void* stream) {
+// Inside b200moe_forward the two BF16 tensor-core GEMMs are chained through per-expert counters.
+static bool chain_stages(const B200MoePlan* p) {
+  static const bool off = std::getenv("B200MOE_NO_CHAIN") != nullptr;
+  return !off && p->schedule == B200MOE_SCHEDULE_TCGEN05 && !p->shape.external_dispatch &&
+         !is_w4(p->shape.gate_up_format) && !is_w4(p->shape.down_format);
+}
+
+static int gate_up_stage(B200MoePlan* p, void* stream, bool chained);
+static int down_stage(B200MoePlan* p, void* stream, bool chained);
+
+int b200moe_gate_up(B200MoePlan* p, void* stream) { return gate_up_stage(p, stream, false); }
+int b200moe_down(B200MoePlan* p, void* stream) { return down_stage(p, stream, false); }
+
+static int gate_up_stage(B200MoePlan* p, void* stream, bool chained) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
@@ -393,10 +408,10 @@ int b200moe_gate_up(B200MoePlan* p, void* stream) {
   // in shared memory above that
   if (is_w4(p->shape.gate_up_format))
     return check_cuda(p->token_tile <= 64 ? launch_gate_up_w4t(*p, s) : launch_gate_up_w4(*p, s), "gate_up launch");
-  return check_cuda(launch_gate_up_tc(*p, s), "gate_up launch");
+  return check_cuda(launch_gate_up_tc(*p, s, chained), "gate_up launch");
 }
 
-int b200moe_down(B200MoePlan* p, void* stream) {
+static int down_stage(B200MoePlan* p, void* stream, bool chained) {
   int rc = require_bound(p);
   if (rc) return rc;
   if (p->shape.tokens == 0) return B200MOE_OK;
@@ -408,7 +423,7 @@ int b200moe_down(B200MoePlan* p, void* stream) {
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
   if (is_w4(p->shape.down_format))
     return check_cuda(p->token_tile <= 64 ? launch_down_w4t(*p, s) : launch_down_w4(*p, s), "down launch");
-  return check_cuda(launch_down_tc(*p, s), "down launch");
+  return check_cuda(launch_down_tc(*p, s, chained), "down launch");
 }
 
 int b200moe_combine(B200MoePlan* p, void* stream) {
@@ -431,8 +446,9 @@ int b200moe_forward(B200MoePlan* p, void* stream) {
   if ((rc = b200moe_router(p, stream))) return rc;
   if ((rc = b200moe_dispatch(p, stream))) return rc;
   if (p && p->shape.route_only) return B200MOE_OK;  // experts run elsewhere; the caller combines later
-  if ((rc = b200moe_gate_up(p, stream))) return rc;
-  if ((rc = b200moe_down(p, stream))) return rc;
+  const bool chained = chain_stages(p);
+  if ((rc = gate_up_stage(p, stream, chained))) return rc;
+  if ((rc = down_stage(p, stream, chained))) return rc;
   return b200moe_combine(p, stream);
 }
 

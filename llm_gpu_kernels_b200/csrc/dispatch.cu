@@ -34,7 +34,8 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kMaxExperts = 256;
 constexpr int kFusedIters = kFusedRoutes / 1024;  // routes per lane of the one-block kernel
 
-// scratch layout: int32 hist[partitions][E], int32 flags[blocks], int32 router_flag
+// scratch layout: int32 hist[partitions][E], int32 flags[blocks], int32 router_flag,
+// then (plans only) int32 tile counter and int32 done[E] of the chained GEMM kernels
 template <typename IdT>
 __global__ void __launch_bounds__(kThreads)
 dispatch_count_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(kMaxExperts)
 dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int* __restrict__ counts,
                      int* __restrict__ offsets, int* __restrict__ cursors, int* __restrict__ tasks,
                      int* __restrict__ status, int* __restrict__ router_flag, int E, int partitions, int blocks,
-                     int token_tile) {
+                     int token_tile, int chain_words) {
   pdl_launch_dependents();
   pdl_wait();  // partition histograms come from the count kernel
   __shared__ int s_scan[16];
@@ -143,6 +144,8 @@ dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int*
     tasks[e] = toff;
     if (e == E - 1) tasks[E] = ttotal;
   }
+  // tile counter and per-expert completion counters of the chained GEMM kernels
+  for (int i = e; i < chain_words; i += blockDim.x) router_flag[1 + i] = 0;
   if (e == 0) {  // the status word restarts every forward; fold in what the router raised
     *status = s_flags | *router_flag;
     *router_flag = 0;
@@ -156,7 +159,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
                       int* __restrict__ mapping, int* __restrict__ counts, int* __restrict__ offsets,
                       int* __restrict__ cursors, int* __restrict__ tasks, int* __restrict__ status,
                       int* __restrict__ router_flag, const int* __restrict__ valid_routes, int R, int E,
-                      int warp_routes, int token_tile) {
+                      int warp_routes, int token_tile, int chain_words) {
   pdl_launch_dependents();
   pdl_wait();  // ids / routing weights may come from the router kernel just before
   const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
@@ -219,6 +222,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
     s_off[e] = off;
     if (e == E - 1) tasks[E] = ttotal;
   }
+  for (int i = e; i < chain_words; i += blockDim.x) router_flag[1 + i] = 0;  // see the scan kernel
   if (e == 0) {
     *status = s_flags | *router_flag;
     *router_flag = 0;
@@ -321,11 +325,11 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     if (sh.ids_are_int64) {
       launch_pdl(dispatch_fused_kernel<long long>, dim3(1), dim3(1024), 0, s, static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
                                                           counts, offsets, cursors, tasks, status, router_flag, valid, R,
-                                                          E, p.warp_routes, p.token_tile);
+                                                          E, p.warp_routes, p.token_tile, p.chain_words);
     } else {
       launch_pdl(dispatch_fused_kernel<int>, dim3(1), dim3(1024), 0, s, static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
                                                     offsets, cursors, tasks, status, router_flag, valid, R, E,
-                                                    p.warp_routes, p.token_tile);
+                                                    p.warp_routes, p.token_tile, p.chain_words);
     }
     if (sh.route_only != 2)  // 2: the rows are sent straight to their expert owners instead
       launch_pdl(dispatch_copy_kernel, dim3((R + kWarps - 1) / kWarps), dim3(kThreads), 0, s,
@@ -343,7 +347,7 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
   launch_pdl(dispatch_scan_kernel, dim3(1), dim3(kMaxExperts), 0, s,
       hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
       static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status),
-      hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile);
+      hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile, p.chain_words);
   const int pblocks = (R + kWarps - 1) / kWarps;
   auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
   auto* grouped = sh.route_only == 2 ? nullptr : static_cast<__nv_bfloat16*>(p.buf.grouped_input);

@@ -26,6 +26,13 @@
 //    epilogue (one TMEM lane quarter each). Shared-memory stages and the TMEM
 //    accumulators are double buffered through mbarriers; every wait is bounded
 //    and on expiry raises B200MOE_STATUS_TIMEOUT and leaves cleanly.
+//  * Inside one forward the two GEMMs are chained by per-expert completion
+//    counters instead of a kernel boundary: every gate/up epilogue warp bumps
+//    done[expert] after its stores, the down kernel is launched as a programmatic
+//    dependent, does not wait for the gate/up grid, takes its tiles from a global
+//    counter (so CTAs that start early do more) and waits per expert until the
+//    counter says that all activated rows of that expert are written. The SMs that
+//    idle in gate/up's last, partial round of tiles stream down weights meanwhile.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
@@ -43,6 +50,8 @@ constexpr int kThreads = 192;
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
+constexpr int kItemRing = 16;  // tiles a dynamic producer may announce ahead of the epilogue
+static_assert(kItemRing >= kMaxStages + 3, "producer could lap the item ring");
 
 struct Ctrl {
   uint64_t full[kMaxStages];
@@ -50,19 +59,45 @@ struct Ctrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
+  uint64_t item_ready[kItemRing];
+  int item[kItemRing];
   uint32_t tmem_base;
   int abort;
   Tables tables;
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
+// Acquire load of a completion counter another SM bumps.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The tile a role works on next. Static schedule: tile seq of this CTA is blockIdx.x + seq * gridDim.x.
+// Dynamic schedule: the producer draws tiles from a global counter and announces them in a small ring
+// that the MMA thread and the epilogue warps follow; -1 ends the work.
+__device__ __forceinline__ int follow_item(Ctrl* c, bool dynamic, int seq, int total_items, int* status) {
+  if (!dynamic) {
+    const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
+    return item < total_items ? static_cast<int>(item) : -1;
+  }
+  const int q = seq % kItemRing;
+  if (!mbar_wait(&c->item_ready[q], static_cast<uint32_t>((seq / kItemRing) & 1), &c->abort, status)) return -1;
+  return *reinterpret_cast<volatile int*>(&c->item[q]);
+}
+
+// chain_done: per-expert completion counters of the gate/up stage (null = stages separated by kernel
+// boundaries). The gate/up kernel adds one per epilogue warp and tile; the down kernel, given
+// chain_need = arrivals per token tile of an expert, waits for them before it loads activated rows.
+// tile_counter (down kernel only): global tile counter of the dynamic schedule, zero at launch.
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_act,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ g_offsets,
                        const int* __restrict__ g_counts, const int* __restrict__ g_tasks, int* __restrict__ status,
                        int E, int n_out, int k_dim, int w_rows_per_expert, int token_tile, int num_stages,
-                       int stream_weights) {
+                       int stream_weights, int* chain_done, int chain_need, int* tile_counter) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -75,9 +110,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
+  const bool chained = !kGateUp && chain_done != nullptr;  // down kernel reading a gate/up grid still running
+  const bool dynamic = !kGateUp && tile_counter != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_launch_dependents();
+  if (!kGateUp) pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(&c->full[s], 1);
@@ -87,6 +124,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       mbar_init(&c->tmem_full[a], 1);
       mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
+    for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
     mbar_init(&c->drain, 1);
     c->abort = 0;
     mbar_init_fence();
@@ -94,7 +132,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (warp == 1) {
     tmem_alloc(&c->tmem_base, tmem_cols);
   }
-  pdl_wait();  // everything above overlapped with the previous kernel; its outputs are needed from here on
+  // Everything above overlapped with the previous kernel. A chained down kernel does not wait for the
+  // gate/up grid: it can only be scheduled after every gate/up CTA has passed its own wait (below), so
+  // the dispatch metadata is complete, and it synchronises on activated rows through chain_done.
+  if (!chained) pdl_wait();
+  // gate/up lets its dependents go only now, so that a chained down kernel inherits "dispatch complete"
+  if (kGateUp) pdl_launch_dependents();
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   tc_fence_before();
   __syncthreads();
@@ -114,9 +157,41 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      int ready_expert = -1;  // activated rows of this expert are known to be complete
+      for (int seq = 0; ok; ++seq) {
+        int item;
+        if (dynamic) {
+          item = atomicAdd(tile_counter, 1);
+          if (item >= total_items) item = -1;
+          const int q = seq % kItemRing;
+          *reinterpret_cast<volatile int*>(&c->item[q]) = item;
+          mbar_arrive(&c->item_ready[q]);  // release: the item is visible to whoever sees the phase flip
+        } else {
+          item = follow_item(c, false, seq, total_items, status);
+        }
+        if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
+        if (chained && t.expert != ready_expert) {
+          const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
+          const unsigned long long start = global_timer();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(chain_done + t.expert) < need) {
+            if ((++spins & 15u) == 0) {
+              if (*reinterpret_cast<volatile int*>(&c->abort)) { ok = false; break; }
+              if (global_timer() - start > kWaitLimitNs) {
+                *reinterpret_cast<volatile int*>(&c->abort) = 1;
+                atomicOr(status, B200MOE_STATUS_TIMEOUT);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          // the rows were written through the generic proxy; the loads below read through the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
+          ready_expert = t.expert;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) { ok = false; break; }
           unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
@@ -143,7 +218,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      for (int seq = 0; ok; ++seq) {
+        const int item = follow_item(c, dynamic, seq, total_items, status);
+        if (item < 0) { ok = !*reinterpret_cast<volatile int*>(&c->abort); break; }
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
         if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
@@ -179,16 +256,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int seq = 0;; ++seq) {
+      // warp-uniform outcomes: the TMEM loads below need the whole warp
+      const int item = follow_item(c, dynamic, seq, total_items, status);
+      if (__any_sync(0xffffffffu, item < 0)) break;
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      // warp-uniform outcome: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
+      if (kGateUp && chain_done != nullptr) __threadfence();  // this lane's rows before the counter
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
+      if (lane == 0) {
+        mbar_arrive(&c->tmem_empty[acc]);
+        if (kGateUp && chain_done != nullptr) atomicAdd(chain_done + t.expert, 1);
+      }
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -211,7 +294,7 @@ int stages_for(bool gate_up, int token_tile, int* smem_bytes) {
 }
 
 template <bool kGateUp>
-cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s) {
+cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
   const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
@@ -227,7 +310,10 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s) {
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
       static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
-      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, stages, stream_weights);
+      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, stages, stream_weights,
+      chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
+      4 * ((sh.intermediate + kTileM - 1) / kTileM),  // epilogue warps x gate/up channel tiles per token tile
+      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr));
   return cudaPeekAtLastError();
 }
 
@@ -253,7 +339,11 @@ int configure_tc(B200MoePlan& p) {
   return B200MOE_OK;
 }
 
-cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s) { return launch_tc<true>(p, s); }
-cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s) { return launch_tc<false>(p, s); }
+cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
+  return launch_tc<true>(p, s, chained);
+}
+cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
+  return launch_tc<false>(p, s, chained);
+}
 
 }  // namespace b200moe

@@ -19,6 +19,7 @@ struct B200MoePlan {
   int warp_routes = 0;
   int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
   bool dispatch_fused = false;  // one-block count + scan + mapping (R <= kFusedRoutes)
+  int chain_words = 0;     // scratch words after the router flag that the dispatch zeroes: tile counter + done[E]
   // TMA descriptors (tcgen05 schedule)
   CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128  (W4: [E*2I, H/8] int32, box 8 x 128)
   CUtensorMap tm_grouped{};     // [R, H] bf16, box 64 x token_tile
@@ -49,8 +50,10 @@ cudaError_t launch_router_tc(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_gate_up_generic(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_generic(const B200MoePlan& p, cudaStream_t s);
-cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s);
-cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s);
+// chained: the two BF16 GEMMs of one forward synchronise per expert through the done[E] counters in
+// scratch and the down kernel draws tiles from the tile counter there (both zeroed by the dispatch).
+cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained);
+cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s);
@@ -68,6 +71,7 @@ int configure_w4t(B200MoePlan& p);
 
 // The router raises its timeout flag in a scratch word (the dispatch folds it into the
 // status word, which it resets every forward): int32 index of that word inside `scratch`.
+// After it: the tile counter of the chained down kernel and done[E], also reset by the dispatch.
 inline size_t router_flag_index(const B200MoePlan& p) {
   const int blocks = (p.partitions + 7) / 8;
   return static_cast<size_t>(p.partitions) * p.shape.experts + blocks;
