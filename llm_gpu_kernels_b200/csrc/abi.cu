@@ -382,6 +382,7 @@ int b200moe_dispatch(B200MoePlan* p, void* stream) {
 }
 
 // Inside b200moe_forward the two BF16 tensor-core GEMMs are chained through per-expert counters.
+static bool w4_in_tmem(const B200MoePlan* p) { return p->token_tile <= 64; }
 static bool chain_stages(const B200MoePlan* p) {
   static const bool off = std::getenv("B200MOE_NO_CHAIN") != nullptr;
   return !off && p->schedule == B200MOE_SCHEDULE_TCGEN05 && !p->shape.external_dispatch &&
@@ -407,7 +408,7 @@ static int gate_up_stage(B200MoePlan* p, void* stream, bool chained) {
   // W4: dequantised operand in tensor memory while two accumulator sets still fit beside it (tile <= 64),
   // in shared memory above that
   if (is_w4(p->shape.gate_up_format))
-    return check_cuda(p->token_tile <= 64 ? launch_gate_up_w4t(*p, s) : launch_gate_up_w4(*p, s), "gate_up launch");
+    return check_cuda(w4_in_tmem(p) ? launch_gate_up_w4t(*p, s) : launch_gate_up_w4(*p, s), "gate_up launch");
   return check_cuda(launch_gate_up_tc(*p, s, chained), "gate_up launch");
 }
 
@@ -422,7 +423,7 @@ static int down_stage(B200MoePlan* p, void* stream, bool chained) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
   if (is_w4(p->shape.down_format))
-    return check_cuda(p->token_tile <= 64 ? launch_down_w4t(*p, s) : launch_down_w4(*p, s), "down launch");
+    return check_cuda(w4_in_tmem(p) ? launch_down_w4t(*p, s) : launch_down_w4(*p, s), "down launch");
   return check_cuda(launch_down_tc(*p, s, chained), "down launch");
 }
 

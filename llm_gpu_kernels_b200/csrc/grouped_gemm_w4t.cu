@@ -17,9 +17,12 @@
 // takes its A operand from there; shared memory only carries the packed words (TMA, 128-byte rows) and the
 // activation rows. That removes the 32 KB store + 36 KB operand fetch per 64 K that made the
 // shared-memory-operand variant (grouped_gemm_w4.cu, used from token tile 128 up, where the accumulators
-// leave no room for two sets plus operand stages in tensor memory) heavy on shared-memory bandwidth. Converter warp w may only touch TMEM lanes 32*(w%4)..+31, so the four warps of a lane
-// quarter split the work of those 32 channels: gate/up tile x half of the 64 K (gate/up), or a quarter of
-// the 64 K each (down).
+// leave no room for two sets plus operand stages in tensor memory) heavy on shared-memory bandwidth.
+// Converter warp w may only touch TMEM lanes 32*(w%4)..+31, so the four warps of a lane quarter share those
+// 32 channel rows by operand stage: warp `part` converts sub-block `part` (64 K) of every 256-K words stage.
+// Measured with work removed selectively (Qwen shape, 17 tokens, gate/up, 128 k-blocks per SM): 98 us as
+// is, 92 without the dequantisation, 69 without the MMAs, 51 with neither: the time is set by the chain
+// convert -> MMA -> completion -> stage free, not by HBM (4x fewer bytes than BF16) or by any one pipe.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
@@ -106,7 +109,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       mbar_init(&c->words_empty[s], kConverters / 32);   // one arrival per converter warp
     }
     for (int s = 0; s < num_operand; ++s) {
-      mbar_init(&c->op_full[s], kConverters / 32 + 1);   // converter warps + the activation TMA
+      mbar_init(&c->op_full[s], 4 + 1);                  // one converter warp per lane quarter + the activation TMA
       mbar_init(&c->op_empty[s], 1);                     // the MMA commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -228,7 +231,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
+      if (!mbar_wait_warp(&c->tmem_full[acc], acc_phase, &c->abort, status)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
@@ -238,65 +241,65 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
-    // ------------------------------------------------------------------ converter warps (6..13)
-    const int quarter = warp & 3;                 // the TMEM lane quarter this warp may write
+    // ------------------------------------------------------------------ converter warps
+    // Warp w may write TMEM lanes 32*(w%4)..+31 only, so the four warps of a lane quarter share those 32
+    // channel rows by operand stage: warp `part` converts sub-block `part` (64 K) of every words stage
+    // (256 K), gate and up rows both. One wait / fence / arrival per 16 words instead of per 4, sixteen
+    // independent words in flight per thread, and four stages are converted at the same time.
+    const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // channel row of the tile = TMEM lane
-    const int part = (warp - 6) >> 2;             // 0..3: which share of the row's 64 K this warp converts
-    // gate/up: part&1 picks the gate or up tile, part>>1 the 16-byte half of the row's 32 packed bytes;
-    // down: part picks a quarter (two words) of the row's 32 packed bytes.
-    const int half = kGateUp ? (part & 1) : 0;
-    const int tid = threadIdx.x - 192;
+    const int part = (warp - 6) >> 2;             // 0..3: the sub-block of each words stage this warp converts
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
-    int p = 0, q = 0;
-    uint32_t pph = 0, qph = 0;
+    int p = 0, gkb = 0;                           // words slot; operand stages issued so far (all warps count)
+    uint32_t pph = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row +
-                       (kGateUp ? half * n_out : 0);
+      long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row;
       if (srow >= total_rows) srow = total_rows - 1;  // lanes past the last channel are never stored
-      const __nv_bfloat16* srow_ptr = scales + srow * groups;
-      __nv_bfloat16 s0 = srow_ptr[0], s1 = srow_ptr[groups > 1 ? 1 : 0];   // the two groups of words stage 0
+      long long srow_up = srow + (kGateUp ? n_out : 0);
+      if (srow_up >= total_rows) srow_up = total_rows - 1;
+      const __nv_bfloat16* sg_ptr = scales + srow * groups + (part >> 1);   // this warp's group inside a words stage
+      const __nv_bfloat16* su_ptr = scales + srow_up * groups + (part >> 1);
+      const bool mine0 = part * kBlockK < min(kWordsK, k_dim);
+      __nv_bfloat16 sg = mine0 ? sg_ptr[0] : __float2bfloat16(0.0f), su = mine0 ? su_ptr[0] : sg;
       for (int ws = 0; ok && ws < num_ws; ++ws) {
-        const __nv_bfloat162 scale_lo = __bfloat162bfloat162(s0), scale_hi = __bfloat162bfloat162(s1);
-        if (ws + 1 < num_ws) {  // prefetch the next stage's scales while this one is converted
-          s0 = srow_ptr[2 * ws + 2];
-          s1 = srow_ptr[min(2 * ws + 3, groups - 1)];
-        }
-        if (!__all_sync(0xffffffffu, mbar_wait(&c->words_full[p], pph, &c->abort, status))) { ok = false; break; }
-        const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes +
-                                     (kGateUp ? half * kWordsTileBytes : 0) + row * 128;
         const int subs = min(kWordsK, k_dim - ws * kWordsK) / kBlockK;
-        for (int j = 0; j < subs; ++j) {
-          if (!__all_sync(0xffffffffu, mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status))) { ok = false; break; }
-          const __nv_bfloat162 scale2 = j < 2 ? scale_lo : scale_hi;
+        const __nv_bfloat162 g2 = __bfloat162bfloat162(sg), u2 = __bfloat162bfloat162(su);
+        if (ws + 1 < num_ws && part * kBlockK < min(kWordsK, k_dim - (ws + 1) * kWordsK)) {
+          sg = sg_ptr[2 * ws + 2];   // next stage's scales while this one is converted
+          su = su_ptr[2 * ws + 2];
+        }
+        if (!mbar_wait_warp(&c->words_full[p], pph, &c->abort, status)) { ok = false; break; }
+        if (part < subs) {
+          const int g = gkb + part;
+          const int q = g % num_operand;
+          const uint32_t qph = static_cast<uint32_t>((g / num_operand) & 1);
+          if (!mbar_wait_warp(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
           tc_fence_after();  // the MMAs that read this stage last have completed (op_empty)
+          const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes + row * 128;
           const uint32_t dst = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols) +
                                (static_cast<uint32_t>(quarter * 32) << 16);
-          if (kGateUp) {
-            const int ch = part >> 1;
-            const uint4 w0 = *reinterpret_cast<const uint4*>(words + (((2 * j + ch) ^ (row & 7)) << 4));
-            const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
+          const int c0 = ((2 * part) ^ (row & 7)) << 4, c1 = ((2 * part + 1) ^ (row & 7)) << 4;
+#pragma unroll 2
+          for (int h = 0; h < (kGateUp ? 4 : 2); ++h) {   // 4 words = 32 K = 16 packed columns per store
+            const __nv_bfloat162 scale2 = h < 2 ? g2 : u2;
+            const uint4 w = *reinterpret_cast<const uint4*>(words + (h >> 1) * kWordsTileBytes + ((h & 1) ? c1 : c0));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
             uint32_t r[16];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 d = dequant_word_t(w[i], scale2);
+              const uint4 d = dequant_word_t(ww[i], scale2);
               r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
             }
-            tmem_st16(dst + half * 32 + ch * 16, r);   // 4 words = 32 K = 16 packed columns
-          } else {
-            const uint2 w0 = *reinterpret_cast<const uint2*>(words + (((2 * j + (part >> 1)) ^ (row & 7)) << 4) +
-                                                             (part & 1) * 8);
-            const uint4 d0 = dequant_word_t(w0.x, scale2), d1 = dequant_word_t(w0.y, scale2);
-            const uint32_t r[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-            tmem_st8(dst + part * 8, r);               // 2 words = 16 K = 8 packed columns
+            tmem_st16(dst + 16 * h, r);
           }
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp
-          if (++q == num_operand) { q = 0; qph ^= 1u; }
+          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp: four warps complete a stage
         }
+        gkb += subs;
         __syncwarp();
         if (lane == 0) mbar_arrive(&c->words_empty[p]);
         if (++p == num_words) { p = 0; pph ^= 1u; }
