@@ -261,7 +261,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       const int item = follow_item(c, dynamic, seq, total_items, status);
       if (__any_sync(0xffffffffu, item < 0)) break;
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      if (!mbar_wait_warp(&c->tmem_full[acc], acc_phase, &c->abort, status)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);

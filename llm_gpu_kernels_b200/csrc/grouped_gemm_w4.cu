@@ -228,7 +228,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      if (!mbar_wait_warp(&c->tmem_full[acc], acc_phase, &c->abort, status)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
@@ -261,12 +261,12 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
           s0 = srow_ptr[2 * ws + 2];
           s1 = srow_ptr[min(2 * ws + 3, groups - 1)];
         }
-        if (!mbar_wait_warp(&c->words_full[p], pph, &c->abort, status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&c->words_full[p], pph, &c->abort, status))) { ok = false; break; }
         const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes +
                                      (kGateUp ? half * kWordsTileBytes : 0) + row * 128;
         const int subs = min(kWordsK, k_dim - ws * kWordsK) / kBlockK;
         for (int j = 0; j < subs; ++j) {
-          if (!mbar_wait_warp(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status))) { ok = false; break; }
           const __nv_bfloat162 scale2 = j < 2 ? scale_lo : scale_hi;
           unsigned char* dst = op_ring + static_cast<size_t>(q) * op_bytes + row * 128;
           if (kGateUp) {

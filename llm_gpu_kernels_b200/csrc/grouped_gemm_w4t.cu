@@ -13,16 +13,18 @@
 // The reference quantises gate/up only; the same format with K = I serves down.
 //
 // This file: the dequantised weight tile never touches shared memory. The converter warps write it
-// with tcgen05.st into tensor memory (channel on the lane, 64 K = 32 packed columns per tile) and the MMA
+// with tcgen05.st into tensor memory (channel on the lane, 128 K = 64 packed columns per tile) and the MMA
 // takes its A operand from there; shared memory only carries the packed words (TMA, 128-byte rows) and the
 // activation rows. That removes the 32 KB store + 36 KB operand fetch per 64 K that made the
 // shared-memory-operand variant (grouped_gemm_w4.cu, used from token tile 128 up, where the accumulators
 // leave no room for two sets plus operand stages in tensor memory) heavy on shared-memory bandwidth.
 // Converter warp w may only touch TMEM lanes 32*(w%4)..+31, so the four warps of a lane quarter share those
-// 32 channel rows by operand stage: warp `part` converts sub-block `part` (64 K) of every 256-K words stage.
-// Measured with work removed selectively (Qwen shape, 17 tokens, gate/up, 128 k-blocks per SM): 98 us as
-// is, 92 without the dequantisation, 69 without the MMAs, 51 with neither: the time is set by the chain
-// convert -> MMA -> completion -> stage free, not by HBM (4x fewer bytes than BF16) or by any one pipe.
+// 32 channel rows by K: warp `part` converts sub-block `part` (64 K) of every 256-K words stage. An operand
+// stage is 128 K (64 TMEM columns per weight tile, two 64-K row tiles in shared memory): the kernel is bound
+// by the chain "stage free -> rows fetched / words converted -> 16 MMAs -> completion -> stage free", not by
+// HBM (4x fewer bytes than BF16) or by any one pipe, so fewer, larger stages are faster. Measured with work
+// removed selectively (Qwen shape, 17 tokens, gate/up, 64-K stages): 98 us as is, 92 without the
+// dequantisation, 69 without the MMAs, 51 with neither; 128-K stages: 86 us.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include "plan.h"
@@ -89,9 +91,9 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
   constexpr uint32_t kOpWeightBytes = 0;  // the weight operand lives in tensor memory
-  constexpr int kACols = kGateUp ? 64 : 32;   // TMEM columns of one operand stage: 64 K packed = 32 columns per tile
+  constexpr int kACols = kGateUp ? 128 : 64;  // TMEM columns of one operand stage: 128 K packed = 64 columns per tile
   constexpr uint32_t kWordsBytes = kGateUp ? 2 * kWordsTileBytes : kWordsTileBytes;  // words stage
-  const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
+  const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 256u;                 // rows x 128 K: two 64-K tiles
   const uint32_t op_bytes = kOpWeightBytes + act_bytes;                               // operand stage
   unsigned char* op_ring = smem_raw + ring_off;
   unsigned char* words_ring = op_ring + static_cast<size_t>(num_operand) * op_bytes;
@@ -109,7 +111,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       mbar_init(&c->words_empty[s], kConverters / 32);   // one arrival per converter warp
     }
     for (int s = 0; s < num_operand; ++s) {
-      mbar_init(&c->op_full[s], 4 + 1);                  // one converter warp per lane quarter + the activation TMA
+      mbar_init(&c->op_full[s], 8 + 1);                  // two converter warps per lane quarter + the activation TMA
       mbar_init(&c->op_empty[s], 1);                     // the MMA commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -174,11 +176,12 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int st = 0; st < num_kb / 2; ++st) {   // one operand stage = 128 K = two 64-K row tiles
           if (!mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
           mbar_expect_tx(&c->op_full[q], act_bytes);
-          tma_load_2d(op_ring + static_cast<size_t>(q) * op_bytes + kOpWeightBytes, &tm_act, &c->op_full[q],
-                      kb * kBlockK, t.row0, pol_act);
+          unsigned char* dst = op_ring + static_cast<size_t>(q) * op_bytes + kOpWeightBytes;
+          tma_load_2d(dst, &tm_act, &c->op_full[q], (2 * st) * kBlockK, t.row0, pol_act);
+          tma_load_2d(dst + act_bytes / 2, &tm_act, &c->op_full[q], (2 * st + 1) * kBlockK, t.row0, pol_act);
           ++issued;
           if (++q == num_operand) { q = 0; qph ^= 1u; }
         }
@@ -201,16 +204,18 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
         tc_fence_after();
         const uint32_t d_gate = tmem_base + static_cast<uint32_t>(acc * acc_cols);
         const uint32_t d_up = d_gate + static_cast<uint32_t>(token_tile);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int st = 0; st < num_kb / 2; ++st) {
           if (!mbar_wait(&c->op_full[q], qph, &c->abort, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_lo = umma_desc_lo(smem_u32(op_ring + static_cast<size_t>(q) * op_bytes));  // activation rows
+          const uint32_t a_half = act_bytes >> 5;   // second 64-K row tile, in 16-byte descriptor units
           const uint32_t w_tmem = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols);                 // weight tile(s)
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16: 8 TMEM columns / 2 descriptor units
-            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
-            umma_tmem_a(d_gate, w_tmem + 8 * k, a_lo + 2 * k, idesc, acc_flag);
-            if (kGateUp) umma_tmem_a(d_up, w_tmem + 32 + 8 * k, a_lo + 2 * k, idesc, acc_flag);
+          for (int k = 0; k < 2 * kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16: 8 TMEM columns / 2 descriptor units
+            const uint32_t acc_flag = (st | k) != 0 ? 1u : 0u;
+            const uint32_t b_lo = a_lo + (k >> 2) * a_half + 2 * (k & 3);
+            umma_tmem_a(d_gate, w_tmem + 8 * k, b_lo, idesc, acc_flag);
+            if (kGateUp) umma_tmem_a(d_up, w_tmem + 64 + 8 * k, b_lo, idesc, acc_flag);
           }
           umma_commit(&c->op_empty[q]);
           if (++q == num_operand) { q = 0; qph ^= 1u; }
@@ -231,7 +236,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-      if (!mbar_wait_warp(&c->tmem_full[acc], acc_phase, &c->abort, status)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
@@ -243,14 +248,14 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
   } else {
     // ------------------------------------------------------------------ converter warps
     // Warp w may write TMEM lanes 32*(w%4)..+31 only, so the four warps of a lane quarter share those 32
-    // channel rows by operand stage: warp `part` converts sub-block `part` (64 K) of every words stage
-    // (256 K), gate and up rows both. One wait / fence / arrival per 16 words instead of per 4, sixteen
-    // independent words in flight per thread, and four stages are converted at the same time.
+    // channel rows by K: warp `part` converts sub-block `part` (64 K) of every words stage (256 K), gate and
+    // up rows both, i.e. half `part & 1` of operand stage `part >> 1` of that words stage. One wait / fence /
+    // arrival per 16 words, sixteen independent words in flight per thread.
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // channel row of the tile = TMEM lane
     const int part = (warp - 6) >> 2;             // 0..3: the sub-block of each words stage this warp converts
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
-    int p = 0, gkb = 0;                           // words slot; operand stages issued so far (all warps count)
+    int p = 0, gst = 0;                           // words slot; operand stages so far (all warps count)
     uint32_t pph = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
@@ -270,12 +275,12 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
           sg = sg_ptr[2 * ws + 2];   // next stage's scales while this one is converted
           su = su_ptr[2 * ws + 2];
         }
-        if (!mbar_wait_warp(&c->words_full[p], pph, &c->abort, status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&c->words_full[p], pph, &c->abort, status))) { ok = false; break; }
         if (part < subs) {
-          const int g = gkb + part;
+          const int g = gst + (part >> 1);
           const int q = g % num_operand;
           const uint32_t qph = static_cast<uint32_t>((g / num_operand) & 1);
-          if (!mbar_wait_warp(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status))) { ok = false; break; }
           tc_fence_after();  // the MMAs that read this stage last have completed (op_empty)
           const unsigned char* words = words_ring + static_cast<size_t>(p) * kWordsBytes + row * 128;
           const uint32_t dst = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols) +
@@ -292,14 +297,15 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
               const uint4 d = dequant_word_t(ww[i], scale2);
               r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
             }
-            tmem_st16(dst + 16 * h, r);
+            // gate columns [0,64) and up columns [64,128) of the stage (down: [0,64)), this warp's 64-K half
+            tmem_st16(dst + (h >> 1) * 64 + (part & 1) * 32 + (h & 1) * 16, r);
           }
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp: four warps complete a stage
+          if (lane == 0) mbar_arrive(&c->op_full[q]);  // one arrival per warp: eight warps complete a stage
         }
-        gkb += subs;
+        gst += subs / 2;
         __syncwarp();
         if (lane == 0) mbar_arrive(&c->words_empty[p]);
         if (++p == num_words) { p = 0; pph ^= 1u; }
@@ -317,11 +323,11 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
 }
 
 void rings_for_t(bool gate_up, int token_tile, int* num_words, int* num_operand, int* smem_bytes) {
-  const int act = token_tile * 128;
+  const int act = token_tile * 256;
   const int words = (gate_up ? 2 : 1) * static_cast<int>(kWordsTileBytes);
-  const int a_cols = gate_up ? 64 : 32, acc_cols = (gate_up ? 2 : 1) * token_tile;
+  const int a_cols = gate_up ? 128 : 64, acc_cols = (gate_up ? 2 : 1) * token_tile;
   int q = kMaxOperand;                                   // operand stages live in TMEM next to the accumulators
-  while (q > 2 && acc_cols + q * a_cols > 512) --q;
+  while (q > 2 && 2 * acc_cols + q * a_cols > 512) --q;  // keep two accumulator sets
   const int budget = kSmemLimit - kCtrlBytes - 1024 - q * act;
   int p = budget / words;
   if (p > kMaxWords) p = kMaxWords;

@@ -59,16 +59,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* a
   }
   return true;
 }
-// The same for a whole warp (every lane must call): lane 0 polls, the others sleep at the warp barrier and
-// then observe the completed phase with one poll of their own (their acquire). Hundreds of threads spinning
-// on try_wait slow every other mbarrier operation of the CTA (TMA completions, the MMA thread's waits).
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* abort, int* status) {
-  bool ok = true;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort, status);
-  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-  if (ok && (threadIdx.x & 31) != 0) ok = mbar_wait(bar, parity, abort, status);
-  return __all_sync(0xffffffffu, ok);
-}
 // Bounded wait with no abort protocol (drain paths).
 __device__ __forceinline__ bool mbar_wait_plain(uint64_t* bar, uint32_t parity) {
   const unsigned long long start = global_timer();
