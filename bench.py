@@ -318,45 +318,10 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
     for _ in range(3):
         e2e_step()
     barrier()
-    e2e_serial_ms = event_ms(e2e_step, steps, stream)
+    # one forward in flight per rank: the ranks' kernels wait on one another, so a second forward on a second
+    # stream could meet its peers in a different order on different ranks
+    e2e_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
-
-    # the same with two forwards in flight: a second prepared layer (own activations and workspace, same
-    # weights) on a second stream, so one step's copies overlap the other step's kernels. Every step still
-    # copies its input from pinned host memory and its result back.
-    slots = [{"x": x, "prepared": prepared, "graph": graph, "x_pinned": x_pinned, "out_pinned": out_pinned,
-              "stream": torch.cuda.Stream(device=dev)}]
-    x2, ids2, rw2 = x.clone(), ids.clone(), rw.clone()
-    prepared2 = build(x2, ids2, rw2)
-    graph2 = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph2, stream=torch.cuda.Stream(device=dev)):
-        prepared2.run()
-    slots.append({"x": x2, "prepared": prepared2, "graph": graph2, "x_pinned": x_host.clone().pin_memory(),
-                  "out_pinned": torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory(),
-                  "stream": torch.cuda.Stream(device=dev)})
-
-    def e2e_pipelined(count):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        for slot in slots:
-            slot["stream"].wait_event(start)
-        for i in range(count):
-            slot = slots[i % 2]
-            with torch.cuda.stream(slot["stream"]):
-                slot["x"].copy_(slot["x_pinned"], non_blocking=True)
-                slot["graph"].replay()
-                slot["out_pinned"].copy_(slot["prepared"].base.output, non_blocking=True)
-        for slot in slots:
-            stream.wait_stream(slot["stream"])
-        end.record(stream)
-        end.synchronize()
-        return start.elapsed_time(end) / count
-
-    e2e_pipelined(6)
-    barrier()
-    e2e_ms = e2e_pipelined(steps)
-    torch.cuda.synchronize(dev)
-    assert torch.equal(slots[1]["out_pinned"], out_pinned), "the two pipeline slots disagree"
     if mode == "nccl":
         launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
         rows, tile = ep.stats.rows_received, ep.backend.expert_plan.token_tile

@@ -68,7 +68,10 @@ typedef struct {
                              2: the same, and dispatch does not copy rows (grouped_input may be NULL) */
   int32_t external_dispatch; /* 1: rows arrive already grouped by expert and counts / offsets / tasks are
                              written by someone else (the expert-owning side of expert parallelism):
-                             forward = gate_up + down on grouped_input; x / ids / weights / output unused */
+                             forward = gate_up + down on grouped_input; x / ids / weights / output unused.
+                             2: the same, and whoever writes the metadata also zeroes the plan's chain words
+                             (b200moe_plan_chain) before every forward, so that gate_up and down may be
+                             chained through them as in an ordinary plan */
   int32_t router_bf16_weights; /* 1: the router rounds its renormalised weights through BF16, as the model the
                              reference captured does (scripts/capture_qwen3_moe_layer0.py:587-588) */
   int32_t reserved[2];
@@ -241,7 +244,17 @@ typedef struct {
   void* return_rows_peers[B200MOE_EP_MAX_RANKS]; /* [tokens*K,H] bf16: down_output of the token plan */
   void* all_counts_peers[B200MOE_EP_MAX_RANKS];  /* [G,E] int32 */
   void* flags_peers[B200MOE_EP_MAX_RANKS];       /* [4*8] int32 barrier flags + [4] local epochs */
+  /* chain words of an expert plan created with external_dispatch = 2 (b200moe_plan_chain), zeroed by
+   * b200moe_ep_exchange_counts every forward; NULL / 0 for external_dispatch = 1 */
+  void* expert_chain;
+  int32_t expert_chain_words;
+  int32_t reserved2;
 } B200MoeEpArgs;
+
+/* The int32 words (inside the bound `scratch` buffer) through which the two BF16 GEMM kernels of one forward
+ * synchronise: a tile counter and one completion counter per expert. An ordinary plan's dispatch zeroes
+ * them; for external_dispatch = 2 the caller must, before every forward. No reference counterpart. */
+int b200moe_plan_chain(B200MoePlan* plan, void** first_word, int32_t* words);
 
 /* int32 entries of B200MoeEpArgs.tables for a given world / experts. */
 size_t b200moe_ep_table_ints(int32_t world, int32_t experts);

@@ -73,7 +73,8 @@ class EpArgs(ctypes.Structure):
         ("reserved", ctypes.c_int32 * 3)] + [(name, ctypes.c_void_p) for name in (
             "x", "ids", "ranks", "counts", "expert_counts", "expert_offsets", "expert_tasks", "expert_rows",
             "expert_output", "tables", "status")] + [(name, ctypes.c_void_p * EP_MAX_RANKS) for name in (
-                "recv_rows_peers", "return_rows_peers", "all_counts_peers", "flags_peers")]
+                "recv_rows_peers", "return_rows_peers", "all_counts_peers", "flags_peers")] + [
+        ("expert_chain", ctypes.c_void_p), ("expert_chain_words", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
 
 
 EXPORTS = {
@@ -89,6 +90,8 @@ EXPORTS = {
     "b200moe_down": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "b200moe_dispatch_static": (ctypes.c_int, [ctypes.POINTER(DispatchArgs), ctypes.c_void_p]),
+    "b200moe_plan_chain": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                          ctypes.POINTER(ctypes.c_int32)]),
     "b200moe_ep_table_ints": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32]),
     "b200moe_peer_alloc": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]),
     "b200moe_peer_free": (ctypes.c_int, [ctypes.c_void_p]),

@@ -385,7 +385,7 @@ int b200moe_dispatch(B200MoePlan* p, void* stream) {
 static bool w4_in_tmem(const B200MoePlan* p) { return p->token_tile <= 64; }
 static bool chain_stages(const B200MoePlan* p) {
   static const bool off = std::getenv("B200MOE_NO_CHAIN") != nullptr;
-  return !off && p->schedule == B200MOE_SCHEDULE_TCGEN05 && !p->shape.external_dispatch &&
+  return !off && p->schedule == B200MOE_SCHEDULE_TCGEN05 && p->shape.external_dispatch != 1 && p->buf.scratch &&
          !is_w4(p->shape.gate_up_format) && !is_w4(p->shape.down_format);
 }
 
@@ -451,6 +451,22 @@ int b200moe_forward(B200MoePlan* p, void* stream) {
   if ((rc = gate_up_stage(p, stream, chained))) return rc;
   if ((rc = down_stage(p, stream, chained))) return rc;
   return b200moe_combine(p, stream);
+}
+
+int b200moe_plan_chain(B200MoePlan* p, void** first_word, int32_t* words) {
+  int rc = require_bound(p);
+  if (rc) return rc;
+  if (!first_word || !words) {
+    set_error("null output pointer");
+    return B200MOE_ERR_INVALID;
+  }
+  if (!p->buf.scratch) {
+    set_error("the plan was bound without a scratch buffer");
+    return B200MOE_ERR_STATE;
+  }
+  *first_word = static_cast<int*>(p->buf.scratch) + router_flag_index(*p) + 1;
+  *words = p->chain_words;
+  return B200MOE_OK;
 }
 
 void b200moe_plan_destroy(B200MoePlan* p) { delete p; }

@@ -77,6 +77,8 @@ ep_counts_kernel(const B200MoeEpArgs a) {
   __shared__ int owner_prefix[kMaxExperts];    // rows of earlier experts of the same owner
   const int E = a.experts, G = a.world, El = E / G, lo = a.rank * El, tid = threadIdx.x;
   const int* counts = static_cast<const int*>(a.counts);
+  // the expert plan's GEMM kernels synchronise through these words and expect them zero at their start
+  for (int i = tid; i < a.expert_chain_words; i += blockDim.x) static_cast<int*>(a.expert_chain)[i] = 0;
   if (tid < E) {
     const int c = counts[tid];
     for (int g = 0; g < G; ++g) static_cast<int*>(a.all_counts_peers[g])[a.rank * E + tid] = c;

@@ -88,6 +88,7 @@ class PreparedMoE:
     token_tile: int = 0
     launches: tuple = ()
     kernel_launches: int = 0  # kernels one run() enqueues
+    chain: tuple = None       # expert-side plans: (device address, count) of the int32 words the exchange zeroes
     _plan: object = field(default=None, repr=False)
     _forward: object = field(default=None, repr=False)
 
@@ -298,7 +299,9 @@ def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, s
 def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None):
     """Plan for the expert-owning side of expert parallelism: rows arrive already grouped by expert in
     ``grouped_input`` ([capacity,H], written by other ranks) and counts / offsets / tasks are written by the
-    exchange kernels; the plan runs gate_up + down only (``launches[2]`` and ``launches[3]``)."""
+    exchange kernels; the plan runs gate_up + down only (``launches[2]`` and ``launches[3]``). The exchange also
+    zeroes the plan's chain words (``plan.chain``: address and count) every forward, which lets the two BF16
+    GEMM kernels overlap as they do in an ordinary plan."""
     capacity, h = grouped_input.shape
     device = grouped_input.device
     dummy_x = grouped_input  # only shapes are taken from it
@@ -309,7 +312,7 @@ def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_sc
     shape = _native.Shape(tokens=capacity, experts=e, topk=1, hidden=h, intermediate=intermediate,
                           gate_up_format=_native.WEIGHTS_BF16 if gate_up_scales is None else _native.WEIGHTS_W4G128,
                           down_format=_native.WEIGHTS_BF16 if down_scales is None else _native.WEIGHTS_W4G128,
-                          schedule=_native.SCHEDULE_AUTO, token_tile=int(token_tile), external_dispatch=1)
+                          schedule=_native.SCHEDULE_AUTO, token_tile=int(token_tile), external_dispatch=2)
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -329,8 +332,13 @@ def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_sc
             counts=ptr(plan.counts), offsets=ptr(plan.offsets), cursors=ptr(plan.cursors), tasks=ptr(plan.tasks),
             grouped_input=ptr(grouped_input), activated=ptr(plan.activated), down_output=ptr(plan.down_output),
             status=ptr(plan.status))
+        plan.scratch = int32((max(1, sizes.scratch // 4),))
+        buffers.scratch = ptr(plan.scratch)
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
+        first, words = ctypes.c_void_p(), ctypes.c_int32()
+        _native.check(lib.b200moe_plan_chain(handle, ctypes.byref(first), ctypes.byref(words)))
+        plan.chain = (first.value, words.value)
     except Exception:
         lib.b200moe_plan_destroy(handle)
         raise
