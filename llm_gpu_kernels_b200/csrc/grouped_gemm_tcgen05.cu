@@ -188,8 +188,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             }
           }
           if (!ok) break;
-          // the rows were written through the generic proxy; the loads below read through the async proxy
-          asm volatile("fence.proxy.async;" ::: "memory");
           ready_expert = t.expert;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -266,7 +264,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
-      if (kGateUp && chain_done != nullptr) __threadfence();  // this lane's rows before the counter
+      if (kGateUp && chain_done != nullptr) {
+        // this lane's rows were written through the generic proxy and the down kernel reads them through the
+        // async proxy (TMA): order them for that proxy, then make them visible GPU-wide before the counter moves
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+      }
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&c->tmem_empty[acc]);
