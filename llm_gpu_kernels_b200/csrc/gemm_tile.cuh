@@ -56,8 +56,10 @@ __device__ __forceinline__ Tile decode_tile(const Tables* c, int item, int E, in
 
 // One epilogue warp drains its 32 TMEM lanes (= 32 output channels) of one tile:
 // D[channel][row] FP32 -> out[row0 + row][channel] BF16, SwiGLU first when kGateUp
-// (gate columns at taddr, up columns at taddr + token_tile). The whole warp must call it.
-template <bool kGateUp>
+// (gate columns at taddr, up columns at taddr + token_tile). kSumPair: the tile was accumulated as two partial
+// sums over K (even and odd K steps, by two MMA-issuing threads) in the same two column ranges; they are added
+// here, in FP32. The whole warp must call it.
+template <bool kGateUp, bool kSumPair = false>
 __device__ __forceinline__ void store_tile(const Tile& t, uint32_t taddr, int token_tile, int channel, int n_out,
                                            __nv_bfloat16* __restrict__ out) {
   const bool ch_ok = channel < n_out;
@@ -65,13 +67,14 @@ __device__ __forceinline__ void store_tile(const Tile& t, uint32_t taddr, int to
   for (int n0 = 0; n0 < t.n_eff; n0 += 16) {
     uint32_t g[16], u[16];
     ptx::tmem_ld16(taddr + n0, g);
-    if (kGateUp) ptx::tmem_ld16(taddr + token_tile + n0, u);
+    if (kGateUp || kSumPair) ptx::tmem_ld16(taddr + token_tile + n0, u);
     ptx::tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const int n = n0 + j;
       float v = __uint_as_float(g[j]);
       if (kGateUp) v = (v / (1.0f + __expf(-v))) * __uint_as_float(u[j]);
+      else if (kSumPair) v = __fadd_rn(v, __uint_as_float(u[j]));
       if (ch_ok && n < t.rows) dst[static_cast<size_t>(n) * n_out] = __float2bfloat16_rn(v);
     }
   }

@@ -39,7 +39,11 @@ using namespace ptx;
 using namespace tile;
 
 constexpr int kConverters = 512;                       // 16 warps (warps 6..21)
-constexpr int kThreads = 192 + kConverters + 32;       // + words TMA, MMA, 4 epilogue, activation TMA warp
+constexpr int kThreads = 192 + kConverters + 64;       // + words TMA, MMA, 4 epilogue, activation TMA, second MMA warp
+// One thread issues a small-N tcgen05.mma about every 100 cycles whatever else the SM does (measured); two threads
+// in different warps issue in parallel. So the MMAs of a stage are split between two issuers with an accumulator
+// each: gate and up tiles (gate/up), even and odd K steps (down; the epilogue adds the two partial sums).
+constexpr int kMmaWarpB = 6 + kConverters / 32 + 1;
 constexpr int kMaxWords = 6, kMaxOperand = 4;
 constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
@@ -53,7 +57,7 @@ struct Ctrl {
   uint64_t op_empty[kMaxOperand];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t drain;
+  uint64_t drain[2];
   uint32_t tmem_base;
   int abort;
   Tables tables;
@@ -97,7 +101,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
   const uint32_t op_bytes = kOpWeightBytes + act_bytes;                               // operand stage
   unsigned char* op_ring = smem_raw + ring_off;
   unsigned char* words_ring = op_ring + static_cast<size_t>(num_operand) * op_bytes;
-  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int acc_cols = 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols + num_operand * kACols <= 512) ? 2 : 1;
   const uint32_t a_col0 = static_cast<uint32_t>(num_acc * acc_cols);       // operand stages follow the accumulators
   uint32_t tmem_cols = 32;
@@ -112,13 +116,14 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     }
     for (int s = 0; s < num_operand; ++s) {
       mbar_init(&c->op_full[s], 8 + 1);                  // two converter warps per lane quarter + the activation TMA
-      mbar_init(&c->op_empty[s], 1);                     // the MMA commit
+      mbar_init(&c->op_empty[s], 2);                     // the commits of the two MMA issuers
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_full[a], 2);  // the two MMA issuers
       mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
-    mbar_init(&c->drain, 1);
+    mbar_init(&c->drain[0], 1);
+    mbar_init(&c->drain[1], 1);
     c->abort = 0;
     mbar_init_fence();
   }
@@ -191,9 +196,10 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
         if (!mbar_wait_plain(&c->op_full[i % num_operand], static_cast<uint32_t>((i / num_operand) & 1))) break;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kMmaWarpB) {
     if (lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
+      // ---------------------------------------------------------------- MMA issuers (0: gate / even K, 1: up / odd K)
+      const int half = warp == 1 ? 0 : 1;
       int q = 0, acc = 0;
       uint32_t qph = 0, acc_phase = 0;
       bool ok = true;
@@ -212,10 +218,12 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
           const uint32_t w_tmem = tmem_base + a_col0 + static_cast<uint32_t>(q * kACols);                 // weight tile(s)
 #pragma unroll
           for (int k = 0; k < 2 * kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16: 8 TMEM columns / 2 descriptor units
-            const uint32_t acc_flag = (st | k) != 0 ? 1u : 0u;
             const uint32_t b_lo = a_lo + (k >> 2) * a_half + 2 * (k & 3);
-            umma_tmem_a(d_gate, w_tmem + 8 * k, b_lo, idesc, acc_flag);
-            if (kGateUp) umma_tmem_a(d_up, w_tmem + 64 + 8 * k, b_lo, idesc, acc_flag);
+            if (kGateUp) {
+              umma_tmem_a(half ? d_up : d_gate, w_tmem + 64 * half + 8 * k, b_lo, idesc, (st | k) != 0 ? 1u : 0u);
+            } else if ((k & 1) == half) {
+              umma_tmem_a(half ? d_up : d_gate, w_tmem + 8 * k, b_lo, idesc, (st | (k >> 1)) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&c->op_empty[q]);
           if (++q == num_operand) { q = 0; qph ^= 1u; }
@@ -225,8 +233,8 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
         if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {
-        umma_commit(&c->drain);
-        mbar_wait_plain(&c->drain, 0);
+        umma_commit(&c->drain[half]);
+        mbar_wait_plain(&c->drain[half], 0);
       }
     }
   } else if (warp < 6) {
@@ -239,7 +247,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
@@ -325,7 +333,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
 void rings_for_t(bool gate_up, int token_tile, int* num_words, int* num_operand, int* smem_bytes) {
   const int act = token_tile * 256;
   const int words = (gate_up ? 2 : 1) * static_cast<int>(kWordsTileBytes);
-  const int a_cols = gate_up ? 128 : 64, acc_cols = (gate_up ? 2 : 1) * token_tile;
+  const int a_cols = gate_up ? 128 : 64, acc_cols = 2 * token_tile;
   int q = kMaxOperand;                                   // operand stages live in TMEM next to the accumulators
   while (q > 2 && 2 * acc_cols + q * a_cols > 512) --q;  // keep two accumulator sets
   const int budget = kSmemLimit - kCtrlBytes - 1024 - q * act;
