@@ -22,8 +22,12 @@
 //  * Tiles are enumerated on the device from the `tasks` prefix the dispatch
 //    wrote (tile -> expert by binary search), round-robin over the persistent
 //    CTAs, so the grid is shape-only and the launch is graph-capturable.
-//  * warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-5 =
-//    epilogue (one TMEM lane quarter each). Shared-memory stages and the TMEM
+//  * warp 0 = TMA producer, warps 1 and 6 = MMA issuers (warp 1 owns TMEM), warps 2-5 =
+//    epilogue (one TMEM lane quarter each). One thread can issue a tcgen05.mma only about
+//    every 100 cycles (measured, any N), two threads in different warps issue in parallel:
+//    the MMAs of a stage are split between two issuers with an accumulator each - the gate
+//    and the up tile, or for the down projection the even and the odd K steps, whose two
+//    partial sums the epilogue adds in FP32. Shared-memory stages and the TMEM
 //    accumulators are double buffered through mbarriers; every wait is bounded
 //    and on expiry raises B200MOE_STATUS_TIMEOUT and leaves cleanly.
 //  * Inside one forward the two GEMMs are chained by per-expert completion
@@ -46,7 +50,8 @@ namespace {
 using namespace ptx;
 using namespace tile;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
+constexpr int kMmaWarpB = 6;  // second MMA-issuing warp
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
@@ -58,7 +63,7 @@ struct Ctrl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t drain;
+  uint64_t drain[2];
   uint64_t item_ready[kItemRing];
   int item[kItemRing];
   uint32_t tmem_base;
@@ -106,7 +111,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   constexpr uint32_t kWBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;
   const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
   const uint32_t stage_bytes = kWBytes + act_bytes;
-  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int acc_cols = 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
@@ -118,14 +123,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(&c->full[s], 1);
-      mbar_init(&c->empty[s], 1);
+      mbar_init(&c->empty[s], 2);   // the commits of the two MMA issuers
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_full[a], 2);  // the two MMA issuers
       mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
     for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
-    mbar_init(&c->drain, 1);
+    mbar_init(&c->drain[0], 1);
+    mbar_init(&c->drain[1], 1);
     c->abort = 0;
     mbar_init_fence();
   }
@@ -210,9 +216,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         if (!mbar_wait_plain(&c->full[s], ph)) { atomicOr(status, B200MOE_STATUS_TIMEOUT); break; }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kMmaWarpB) {
     if (lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
+      // ---------------------------------------------------------------- MMA issuers (0: gate / even K, 1: up / odd K)
+      const int half = warp == 1 ? 0 : 1;
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -232,10 +239,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
           const uint32_t a_addr = w_addr + kWBytes;
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
             const uint64_t bdesc = umma_desc(a_addr + k * kUmmaK * 2);
-            umma(d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, acc_flag);
-            if (kGateUp) umma(d_up, umma_desc(w_addr + kWTileBytes + k * kUmmaK * 2), bdesc, idesc, acc_flag);
+            if (kGateUp) {
+              umma(half ? d_up : d_gate, umma_desc(w_addr + half * kWTileBytes + k * kUmmaK * 2), bdesc, idesc,
+                   (kb | k) != 0 ? 1u : 0u);
+            } else if ((k & 1) == half) {
+              umma(half ? d_up : d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, (kb | (k >> 1)) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&c->empty[stage]);  // stage reusable once these MMAs have read it
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -245,8 +255,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {  // gave up: let the MMAs already issued finish before TMEM is freed
-        umma_commit(&c->drain);
-        mbar_wait_plain(&c->drain, 0);
+        umma_commit(&c->drain[half]);
+        mbar_wait_plain(&c->drain[half], 0);
       }
     }
   } else {
@@ -262,7 +272,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
       if (kGateUp && chain_done != nullptr) {
         // this lane's rows were written through the generic proxy and the down kernel reads them through the
