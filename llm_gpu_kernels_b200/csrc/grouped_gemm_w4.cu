@@ -36,7 +36,10 @@ using namespace ptx;
 using namespace tile;
 
 constexpr int kConverters = 512;                       // 16 warps (warps 6..21)
-constexpr int kThreads = 192 + kConverters + 32;       // + words TMA, MMA, 4 epilogue, activation TMA warp
+constexpr int kThreads = 192 + kConverters + 64;       // + words TMA, MMA, 4 epilogue, activation TMA, second MMA warp
+// Two MMA-issuing threads with an accumulator each (one thread issues a tcgen05.mma only about every 100 cycles):
+// the gate and the up tile, or for down the even and the odd K steps, summed in the epilogue.
+constexpr int kMmaWarpB = 6 + kConverters / 32 + 1;
 constexpr int kMaxWords = 6, kMaxOperand = 4;
 constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
@@ -50,7 +53,7 @@ struct Ctrl {
   uint64_t op_empty[kMaxOperand];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t drain;
+  uint64_t drain[2];
   uint32_t tmem_base;
   int abort;
   Tables tables;
@@ -93,7 +96,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   const uint32_t op_bytes = kOpWeightBytes + act_bytes;                               // operand stage
   unsigned char* op_ring = smem_raw + ring_off;
   unsigned char* words_ring = op_ring + static_cast<size_t>(num_operand) * op_bytes;
-  const int acc_cols = kGateUp ? 2 * token_tile : token_tile;
+  const int acc_cols = 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
@@ -107,13 +110,14 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     }
     for (int s = 0; s < num_operand; ++s) {
       mbar_init(&c->op_full[s], kConverters / 32 + 1);   // converter warps + the activation TMA
-      mbar_init(&c->op_empty[s], 1);                     // the MMA commit
+      mbar_init(&c->op_empty[s], 2);                     // the commits of the two MMA issuers
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&c->tmem_full[a], 1);
+      mbar_init(&c->tmem_full[a], 2);  // the two MMA issuers
       mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
-    mbar_init(&c->drain, 1);
+    mbar_init(&c->drain[0], 1);
+    mbar_init(&c->drain[1], 1);
     c->abort = 0;
     mbar_init_fence();
   }
@@ -185,9 +189,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
         if (!mbar_wait_plain(&c->op_full[i % num_operand], static_cast<uint32_t>((i / num_operand) & 1))) break;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kMmaWarpB) {
     if (lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
+      // ---------------------------------------------------------------- MMA issuers (0: gate / even K, 1: up / odd K)
+      const int half = warp == 1 ? 0 : 1;
       int q = 0, acc = 0;
       uint32_t qph = 0, acc_phase = 0;
       bool ok = true;
@@ -205,9 +210,12 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
           const uint32_t w_lo = umma_desc_lo(w_addr), a_lo = umma_desc_lo(w_addr + kOpWeightBytes);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {  // a K step of 16 BF16 = 32 bytes = 2 in descriptor units
-            const uint32_t acc_flag = (kb | k) != 0 ? 1u : 0u;
-            umma_lo(d_gate, w_lo + 2 * k, a_lo + 2 * k, idesc, acc_flag);
-            if (kGateUp) umma_lo(d_up, w_lo + (kWTileBytes >> 4) + 2 * k, a_lo + 2 * k, idesc, acc_flag);
+            if (kGateUp) {
+              umma_lo(half ? d_up : d_gate, w_lo + half * (kWTileBytes >> 4) + 2 * k, a_lo + 2 * k, idesc,
+                      (kb | k) != 0 ? 1u : 0u);
+            } else if ((k & 1) == half) {
+              umma_lo(half ? d_up : d_gate, w_lo + 2 * k, a_lo + 2 * k, idesc, (kb | (k >> 1)) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&c->op_empty[q]);
           if (++q == num_operand) { q = 0; qph ^= 1u; }
@@ -217,8 +225,8 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
         if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {
-        umma_commit(&c->drain);
-        mbar_wait_plain(&c->drain, 0);
+        umma_commit(&c->drain[half]);
+        mbar_wait_plain(&c->drain[half], 0);
       }
     }
   } else if (warp < 6) {
@@ -231,7 +239,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      store_tile<kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
