@@ -124,6 +124,9 @@ typedef struct {
   void* scratch;
   const void* valid_routes;    /* optional device int32: only the first *valid_routes routes exist this forward
                                   (the rest of the fixed-capacity buffers is padding); NULL = all T*K */
+  const void* residual;        /* optional [T,H] bf16: output = bf16(float(residual) + float(bf16(layer result))),
+                                  i.e. the layer followed by the model's residual add in BF16, in the combine kernel.
+                                  May alias `output` is NOT allowed; NULL = no residual. No reference counterpart. */
 } B200MoeBuffers;
 
 /* ABI version of the loaded library. */

@@ -50,7 +50,7 @@ INPUT_BUFFERS = ("x", "router_weight", "gate_up", "gate_up_scales", "down", "dow
 
 
 class Buffers(ctypes.Structure):
-    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS + ("valid_routes",)]
+    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS + ("valid_routes", "residual")]
 
 
 class DispatchArgs(ctypes.Structure):

@@ -301,7 +301,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
       return B200MOE_ERR_INVALID;
     }
     // the output and the workspace must not alias the inputs (cuda_gate_up.cu:150-158)
-    const void* inputs[] = {b->x, b->gate_up, b->down, b->ids, b->routing_weights, b->router_weight};
+    const void* inputs[] = {b->x, b->gate_up, b->down, b->ids, b->routing_weights, b->router_weight, b->residual};
     const void* written[] = {b->output, b->grouped_input, b->activated, b->down_output, b->mapping, b->ranks};
     for (const void* in : inputs)
       for (const void* wr : written)

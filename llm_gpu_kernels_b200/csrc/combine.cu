@@ -5,6 +5,8 @@
 // enable_fp_fusion=False at moe.py:217). A gather-reduce, not a scatter with
 // atomics, so the result does not depend on scheduling. Routes with
 // mapping < 0 (invalid expert id) contribute nothing (moe.py:117).
+// Optional residual: out = bf16(float(residual[t,:]) + float(bf16(sum))) - what the layer followed by the
+// model's BF16 residual add gives, without writing and re-reading the layer output.
 #include <cuda_bf16.h>
 #include "plan.h"
 #include "pdl.cuh"
@@ -18,7 +20,7 @@ template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict__ mapping,
                const float* __restrict__ rw, __nv_bfloat16* __restrict__ out, const int* __restrict__ valid_routes,
-               int H, int K) {
+               const __nv_bfloat16* __restrict__ residual, int H, int K) {
   pdl_launch_dependents();
   pdl_wait();  // down_output / mapping come from the kernels before
   const int token = blockIdx.x;
@@ -63,6 +65,17 @@ combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict
       const __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
       ou[j] = *reinterpret_cast<const uint32_t*>(&v);
     }
+    if (residual) {
+      const uint4 r = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(token) * H + h);
+      const uint32_t ru[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(
+            __fadd_rn(__uint_as_float(ru[j] << 16), __uint_as_float(ou[j] << 16)),
+            __fadd_rn(__uint_as_float(ru[j] & 0xffff0000u), __uint_as_float(ou[j] & 0xffff0000u)));
+        ou[j] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    }
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(token) * H + h) = o;
   } else {
     const int h = blockIdx.y * kThreads + threadIdx.x;
@@ -73,7 +86,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ down_out, const int* __restrict
       if (pos < 0) continue;
       acc = __fadd_rn(acc, __fmul_rn(__bfloat162float(down_out[static_cast<size_t>(pos) * H + h]), s_w[slot]));
     }
-    out[static_cast<size_t>(token) * H + h] = __float2bfloat16_rn(acc);
+    __nv_bfloat16 r = __float2bfloat16_rn(acc);
+    if (residual)
+      r = __float2bfloat16_rn(__fadd_rn(__bfloat162float(residual[static_cast<size_t>(token) * H + h]), __bfloat162float(r)));
+    out[static_cast<size_t>(token) * H + h] = r;
   }
 }
 
@@ -83,18 +99,19 @@ cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s) {
   const auto& sh = p.shape;
   auto* d = static_cast<const __nv_bfloat16*>(p.buf.down_output);
   auto* o = static_cast<__nv_bfloat16*>(p.buf.output);
+  auto* res = static_cast<const __nv_bfloat16*>(p.buf.residual);
   const bool vec = sh.hidden % 8 == 0 &&
-                   ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(o)) & 15) == 0;
+                   ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(res)) & 15) == 0;
   if (vec) {
     dim3 grid(sh.tokens, (sh.hidden / 8 + kThreads - 1) / kThreads);
     launch_pdl(combine_kernel<true>, grid, dim3(kThreads), 0, s, d, static_cast<const int*>(p.buf.mapping),
                                                    static_cast<const float*>(p.buf.routing_weights), o,
-                                                   static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
+                                                   static_cast<const int*>(p.buf.valid_routes), res, sh.hidden, sh.topk);
   } else {
     dim3 grid(sh.tokens, (sh.hidden + kThreads - 1) / kThreads);
     launch_pdl(combine_kernel<false>, grid, dim3(kThreads), 0, s, d, static_cast<const int*>(p.buf.mapping),
                                                     static_cast<const float*>(p.buf.routing_weights), o,
-                                                    static_cast<const int*>(p.buf.valid_routes), sh.hidden, sh.topk);
+                                                    static_cast<const int*>(p.buf.valid_routes), res, sh.hidden, sh.topk);
   }
   return cudaPeekAtLastError();
 }

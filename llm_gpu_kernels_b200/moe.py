@@ -84,6 +84,7 @@ class PreparedMoE:
     down_scales: torch.Tensor = None     # set when down holds packed W4G128 words
     packed: object = None                # the PackedGateUp the plan was prepared from (reference W4Workspace.packed)
     valid_routes: torch.Tensor = None    # optional device int32: routes beyond it are padding this forward
+    residual: torch.Tensor = None        # optional [T,H] bf16 added to the layer result in the combine kernel
     schedule: str = ""
     token_tile: int = 0
     launches: tuple = ()
@@ -209,7 +210,7 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
              route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None,
-             router_bf16_weights=False):
+             router_bf16_weights=False, residual=None):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
@@ -222,6 +223,9 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         raise ValueError("valid_routes must be one int32 on the same device")
     if schedule not in _SCHEDULES:
         raise ValueError(f"unknown schedule {schedule!r}; expected one of auto/generic/tcgen05")
+    if residual is not None and (residual.dtype != torch.bfloat16 or residual.shape != x.shape
+                                 or residual.device != x.device or not residual.is_contiguous()):
+        raise ValueError("residual must be a contiguous bfloat16 tensor of the shape and device of x")
     lib = _native.load()
     tokens = x.shape[0]
     topk = ids.shape[1]
@@ -252,7 +256,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
             kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
-            valid_routes=valid_routes)
+            valid_routes=valid_routes, residual=residual)
         for name, tensor in (workspace or {}).items():  # caller-provided workspace (peer-visible buffers)
             if tuple(tensor.shape) != tuple(getattr(plan, name).shape) or tensor.dtype != getattr(plan, name).dtype:
                 raise ValueError(f"workspace override {name} has the wrong shape or dtype")
@@ -268,7 +272,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         buffers = _native.Buffers(
             x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales),
             down=ptr(down), down_scales=ptr(down_scales), ids=ptr(ids), routing_weights=ptr(routing_weights),
-            valid_routes=ptr(valid_routes),
+            valid_routes=ptr(valid_routes), residual=ptr(residual),
             **{name: ptr(tensor) for name, tensor in expected.items()})
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
@@ -289,11 +293,13 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
 
 
 def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0,
-                router_bf16_weights=False):
+                router_bf16_weights=False, residual=None):
     """Drop-in for reference ``prepare_moe`` (moe.py:220-245). ``router_bf16_weights`` makes the router round
-    its weights through BF16 like the captured model does (scripts/capture_qwen3_moe_layer0.py:587-588)."""
+    its weights through BF16 like the captured model does (scripts/capture_qwen3_moe_layer0.py:587-588).
+    ``residual`` ([T,H] bf16, read every forward) is added to the layer result inside the combine kernel:
+    ``output = bf16(residual + bf16(layer))``, the model's residual add without a round trip through HBM."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
-                    token_tile=token_tile, router_bf16_weights=router_bf16_weights)
+                    token_tile=token_tile, router_bf16_weights=router_bf16_weights, residual=residual)
 
 
 def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None):

@@ -194,6 +194,22 @@ def test_router_bf16_rounded_weights(dev, schedule):
     check_output(out, (x, gate_up, down, ids.cpu(), got))
 
 
+@pytest.mark.parametrize("schedule,h", [(None, 256), ("generic", 100)])
+def test_residual_added_in_combine(dev, schedule, h):
+    """output = bf16(residual + bf16(layer)): bit-identical to the plain layer followed by a BF16 add."""
+    from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    args = make_inputs(45, 8, 3, h, 128 if h == 256 else 72, seed=13, wscale=0.1, device=dev)
+    plain = prepare_ranked_moe_launcher(*args, schedule=schedule).run().clone()
+    residual = torch.randn(45, h, generator=torch.Generator().manual_seed(4)).bfloat16().to(dev)
+    fused = prepare_ranked_moe_launcher(*args, schedule=schedule, residual=residual)
+    want = (residual.float() + plain.float()).bfloat16()
+    assert torch.equal(fused.run(), want)
+    residual.mul_(-2.0)                      # read every forward, not captured at prepare time
+    assert torch.equal(fused.run(), (residual.float() + plain.float()).bfloat16())
+    with pytest.raises(ValueError):
+        prepare_ranked_moe_launcher(*args, residual=residual.float())
+
+
 def test_tiny_layer_golden(dev, golden_dir):
     """BASELINE config 1 against the reference's own output on the same seeded inputs."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
