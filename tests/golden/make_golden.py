@@ -135,4 +135,6 @@ def main(ref_root):
 
 if __name__ == "__main__":
     sys.path.insert(0, str(HERE.parents[1]))
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to a checkout of the reference project>")
+    main(sys.argv[1])

@@ -123,7 +123,7 @@ def test_qwen_shape_full_layer(dev, tokens):
     ok, msg = O.router_agrees(ids_cpu, rw_cpu, probs, 8)
     assert ok, msg
     check_dispatch(p.base, x, ids_cpu, 128)
-    # experts are judged on the routes the device chose (ties between FP32 orders are legal)
+    # experts are compared on the routes the device chose (ties between FP32 orders are legal)
     m = check_output(out, (x, gate_up, down, ids_cpu, rw_cpu))
     print(f"T={tokens} rel_rms={m['relative_rms']:.2e} norm_max={m['normalized_max']:.2e}")
     # determinism: three runs, identical bits
