@@ -100,3 +100,46 @@ def test_two_rank_expert_parallel(shape):
     result = mp.Manager().dict()
     mp.spawn(_run_rank, args=(2, 29743, shape, result), nprocs=2, join=True)
     assert sum(v[1] for v in result.values()) == 2 * shape[0] * shape[2]
+
+
+def test_absent_peer_is_reported_not_waited_for():
+    """A rank whose peer never arrives: the count exchange's barrier gives up after its 1 s bound, raises status
+    bit 4 (a bounded wait ran out) and returns; the context stays usable. The "peer" is a second set of local
+    buffers that nothing ever writes - no second process, no second kernel."""
+    import ctypes
+    import time
+    from llm_gpu_kernels_b200 import _native
+    from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
+    lib = _native.load()
+    dev = torch.device("cuda:0")
+    experts, topk, hidden, tokens, capacity = 8, 2, 128, 16, 64
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)
+    bf16 = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    x, ids, ranks, counts, status = bf16(tokens, hidden), i32(tokens * topk), i32(tokens * topk), i32(experts), i32(1)
+    keep = dict(ec=i32(experts), eo=i32(experts), et=i32(experts + 1), er=i32(1), out=bf16(capacity, hidden),
+                tables=i32(int(lib.b200moe_ep_table_ints(2, experts))))
+    peers = {name: [make() for _ in range(2)] for name, make in (
+        ("recv_rows_peers", lambda: bf16(capacity, hidden)), ("return_rows_peers", lambda: bf16(tokens * topk, hidden)),
+        ("all_counts_peers", lambda: i32(2 * experts)), ("flags_peers", lambda: i32(64)))}
+    args = _native.EpArgs(rank=0, world=2, experts=experts, topk=topk, hidden=hidden, tokens=tokens,
+                          capacity=capacity, token_tile=16, ids_are_int64=0, x=ptr(x), ids=ptr(ids), ranks=ptr(ranks),
+                          counts=ptr(counts), expert_counts=ptr(keep["ec"]), expert_offsets=ptr(keep["eo"]),
+                          expert_tasks=ptr(keep["et"]), expert_rows=ptr(keep["er"]), expert_output=ptr(keep["out"]),
+                          tables=ptr(keep["tables"]), status=ptr(status))
+    for field, buffers in peers.items():
+        for g in range(2):
+            getattr(args, field)[g] = buffers[g].data_ptr()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    torch.cuda.synchronize()
+    start = time.time()
+    _native.check(lib.b200moe_ep_exchange_counts(ctypes.byref(args), stream))
+    torch.cuda.synchronize()
+    waited = time.time() - start
+    assert int(status) & 4, "the barrier must report that its wait ran out"
+    assert 0.5 < waited < 10.0, waited
+    # the context is intact: an ordinary layer still runs and checks out
+    layer = make_inputs(20, 4, 2, 128, 64, seed=2, wscale=0.1, device=dev)
+    prepared = prepare_ranked_moe_launcher(*layer)
+    prepared.run()
+    prepared.check_inputs()
