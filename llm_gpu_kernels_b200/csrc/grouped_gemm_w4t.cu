@@ -49,6 +49,7 @@ constexpr int kWordsK = 256;                           // K covered by one words
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
 constexpr uint32_t kWordsTileBytes = kTileM * kWordsK / 2;  // one packed tile of 256 K: 16 KB
 constexpr int kCtrlBytes = 4096;
+constexpr int kItemRing = 16;   // tiles the dynamic schedule may announce ahead of the epilogue (see follow_item)
 
 struct Ctrl {
   uint64_t words_full[kMaxWords];
@@ -58,6 +59,8 @@ struct Ctrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain[2];
+  uint64_t item_ready[kItemRing];
+  int item[kItemRing];
   uint32_t tmem_base;
   int abort;
   Tables tables;
@@ -83,13 +86,39 @@ __device__ __forceinline__ uint4 dequant_word_t(uint32_t w, __nv_bfloat162 scale
   return out;
 }
 
+// Acquire load of a completion counter another SM bumps.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The tile a role works on next. Static schedule: blockIdx.x + seq * gridDim.x. Dynamic schedule (the down kernel
+// chained to a gate/up grid that is still running): the words producer draws tiles from a global counter, so that
+// CTAs that start early do more, and announces them in a small ring every other role follows; -1 ends the work.
+// The producer runs at most the words ring (6 stages) plus the accumulator sets ahead of the epilogue: < 16 tiles.
+__device__ __forceinline__ int follow_item(Ctrl* c, bool dynamic, int seq, int total_items, int* status) {
+  if (!dynamic) {
+    const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
+    return item < total_items ? static_cast<int>(item) : -1;
+  }
+  const int q = seq % kItemRing;
+  if (!mbar_wait(&c->item_ready[q], static_cast<uint32_t>((seq / kItemRing) & 1), &c->abort, status)) return -1;
+  return *reinterpret_cast<volatile int*>(&c->item[q]);
+}
+
+// chain_done / chain_need / tile_counter: as in the BF16 kernel (grouped_gemm_tcgen05.cu). The gate/up kernel adds
+// one to chain_done[expert] per epilogue warp and tile; the down kernel, launched as a programmatic dependent, does
+// not wait for the gate/up grid but, per expert, for chain_need arrivals per token tile before it loads activated
+// rows, and draws its tiles from *tile_counter. Null pointers = stages separated by a kernel boundary.
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __grid_constant__ CUtensorMap tm_act,
                        const __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
                        const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
-                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights) {
+                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights,
+                       int* chain_done, int chain_need, int* tile_counter) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -108,7 +137,9 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
   while (tmem_cols < a_col0 + static_cast<uint32_t>(num_operand * kACols)) tmem_cols <<= 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_launch_dependents();
+  const bool chained = !kGateUp && chain_done != nullptr;
+  const bool dynamic = !kGateUp && tile_counter != nullptr;
+  if (!kGateUp) pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_words; ++s) {
       mbar_init(&c->words_full[s], 1);
@@ -124,11 +155,15 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     }
     mbar_init(&c->drain[0], 1);
     mbar_init(&c->drain[1], 1);
+    for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
     c->abort = 0;
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
-  pdl_wait();  // the previous kernel's outputs are needed from here on
+  // A chained down kernel can only be scheduled once every gate/up CTA has passed its own wait (gate/up lets its
+  // dependents go after it), so the dispatch metadata is complete; activated rows are awaited per expert below.
+  if (!chained) pdl_wait();
+  if (kGateUp) pdl_launch_dependents();
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   tc_fence_before();
   __syncthreads();
@@ -149,7 +184,18 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       uint32_t pph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      for (int seq = 0; ok; ++seq) {
+        int item;
+        if (dynamic) {
+          item = atomicAdd(tile_counter, 1);
+          if (item >= total_items) item = -1;
+          const int q = seq % kItemRing;
+          *reinterpret_cast<volatile int*>(&c->item[q]) = item;
+          mbar_arrive(&c->item_ready[q]);  // release: the item is visible to whoever sees the phase flip
+        } else {
+          item = follow_item(c, false, seq, total_items, status);
+        }
+        if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
         for (int ws = 0; ws < num_ws; ++ws) {
@@ -179,8 +225,29 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       uint32_t qph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      int ready_expert = -1;   // activated rows of this expert are known to be complete
+      for (int seq = 0; ok; ++seq) {
+        const int item = follow_item(c, dynamic, seq, total_items, status);
+        if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        if (chained && t.expert != ready_expert) {
+          const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
+          const unsigned long long start = global_timer();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(chain_done + t.expert) < need) {
+            if ((++spins & 15u) == 0) {
+              if (*reinterpret_cast<volatile int*>(&c->abort)) { ok = false; break; }
+              if (global_timer() - start > kWaitLimitNs) {
+                *reinterpret_cast<volatile int*>(&c->abort) = 1;
+                atomicOr(status, B200MOE_STATUS_TIMEOUT);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          ready_expert = t.expert;
+        }
         for (int st = 0; st < num_kb / 2; ++st) {   // one operand stage = 128 K = two 64-K row tiles
           if (!mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
           mbar_expect_tx(&c->op_full[q], act_bytes);
@@ -203,7 +270,9 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       int q = 0, acc = 0;
       uint32_t qph = 0, acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      for (int seq = 0; ok; ++seq) {
+        const int item = follow_item(c, dynamic, seq, total_items, status);
+        if (item < 0) { ok = !*reinterpret_cast<volatile int*>(&c->abort); break; }
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
         if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
@@ -242,15 +311,25 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     const int quarter = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int seq = 0;; ++seq) {
+      const int item = follow_item(c, dynamic, seq, total_items, status);
+      if (__any_sync(0xffffffffu, item < 0)) break;   // warp-uniform: the TMEM loads below need the whole warp
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
+      if (kGateUp && chain_done != nullptr) {
+        // this lane's rows: ordered for the async proxy (the down kernel reads them by TMA), then visible GPU-wide
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
+      if (lane == 0) {
+        mbar_arrive(&c->tmem_empty[acc]);
+        if (kGateUp && chain_done != nullptr) atomicAdd(chain_done + t.expert, 1);
+      }
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
@@ -266,7 +345,9 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     int p = 0, gst = 0;                           // words slot; operand stages so far (all warps count)
     uint32_t pph = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+    for (int seq = 0; ok; ++seq) {
+      const int item = follow_item(c, dynamic, seq, total_items, status);
+      if (__any_sync(0xffffffffu, item < 0)) break;
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
       long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row;
       if (srow >= total_rows) srow = total_rows - 1;  // lanes past the last channel are never stored
@@ -345,7 +426,7 @@ void rings_for_t(bool gate_up, int token_tile, int* num_words, int* num_operand,
 }
 
 template <bool kGateUp>
-cudaError_t launch_w4t(const B200MoePlan& p, cudaStream_t s) {
+cudaError_t launch_w4t(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
   const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
@@ -361,7 +442,10 @@ cudaError_t launch_w4t(const B200MoePlan& p, cudaStream_t s) {
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
       static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
       kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, kGateUp ? p.w4t_packed_gate_up : p.w4t_packed_down,
-      kGateUp ? p.w4t_operand_gate_up : p.w4t_operand_down, stream_weights);
+      kGateUp ? p.w4t_operand_gate_up : p.w4t_operand_down, stream_weights,
+      chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
+      4 * ((sh.intermediate + kTileM - 1) / kTileM),  // epilogue warps x gate/up channel tiles per token tile
+      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr));
   return cudaPeekAtLastError();
 }
 
@@ -385,7 +469,9 @@ int configure_w4t(B200MoePlan& p) {
   return B200MOE_OK;
 }
 
-cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s) { return launch_w4t<true>(p, s); }
-cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s) { return launch_w4t<false>(p, s); }
+cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s, bool chained) {
+  return launch_w4t<true>(p, s, chained);
+}
+cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s, bool chained) { return launch_w4t<false>(p, s, chained); }
 
 }  // namespace b200moe

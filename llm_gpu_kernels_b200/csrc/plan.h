@@ -56,8 +56,8 @@ cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s);
 cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s);
-cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s);
-cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
+cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
 
 size_t router_smem_bytes(int hidden, int experts);
