@@ -387,8 +387,7 @@ static bool chain_stages(const B200MoePlan* p) {
   static const bool off = std::getenv("B200MOE_NO_CHAIN") != nullptr;
   if (off || p->schedule != B200MOE_SCHEDULE_TCGEN05 || p->shape.external_dispatch == 1 || !p->buf.scratch) return false;
   const bool g4 = is_w4(p->shape.gate_up_format), d4 = is_w4(p->shape.down_format);
-  // both stages on the BF16 kernel, or both on the W4 kernel that keeps its operand in tensor memory
-  return g4 == d4 && (!g4 || w4_in_tmem(p));
+  return g4 == d4;   // both stages BF16 or both W4 (the two W4 variants are chosen by token tile, the same for both)
 }
 
 static int gate_up_stage(B200MoePlan* p, void* stream, bool chained);
@@ -410,7 +409,7 @@ static int gate_up_stage(B200MoePlan* p, void* stream, bool chained) {
   // W4: dequantised operand in tensor memory while two accumulator sets still fit beside it (tile <= 64),
   // in shared memory above that
   if (is_w4(p->shape.gate_up_format))
-    return check_cuda(w4_in_tmem(p) ? launch_gate_up_w4t(*p, s, chained) : launch_gate_up_w4(*p, s), "gate_up launch");
+    return check_cuda(w4_in_tmem(p) ? launch_gate_up_w4t(*p, s, chained) : launch_gate_up_w4(*p, s, chained), "gate_up launch");
   return check_cuda(launch_gate_up_tc(*p, s, chained), "gate_up launch");
 }
 
@@ -425,7 +424,7 @@ static int down_stage(B200MoePlan* p, void* stream, bool chained) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
   if (is_w4(p->shape.down_format))
-    return check_cuda(w4_in_tmem(p) ? launch_down_w4t(*p, s, chained) : launch_down_w4(*p, s), "down launch");
+    return check_cuda(w4_in_tmem(p) ? launch_down_w4t(*p, s, chained) : launch_down_w4(*p, s, chained), "down launch");
   return check_cuda(launch_down_tc(*p, s, chained), "down launch");
 }
 

@@ -54,6 +54,60 @@ __device__ __forceinline__ Tile decode_tile(const Tables* c, int item, int E, in
   return t;
 }
 
+// Chaining of the gate/up and the down kernel of one forward (see grouped_gemm_tcgen05.cu): the down kernel does not
+// wait for the gate/up grid but for per-expert completion counters, and draws its tiles from a global counter.
+constexpr int kItemRing = 16;  // tiles a dynamic producer may announce ahead of the epilogue
+
+// Acquire load of a completion counter another SM bumps.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The tile a role works on next. Static schedule: tile seq of this CTA is blockIdx.x + seq * gridDim.x.
+// Dynamic schedule: the producer draws tiles from a global counter and announces them in a small ring
+// (Ctrl::item / Ctrl::item_ready, kItemRing entries) that the other roles follow; -1 ends the work.
+template <class Ctrl>
+__device__ __forceinline__ int follow_item(Ctrl* c, bool dynamic, int seq, int total_items, int* status) {
+  if (!dynamic) {
+    const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
+    return item < total_items ? static_cast<int>(item) : -1;
+  }
+  const int q = seq % kItemRing;
+  if (!ptx::mbar_wait(&c->item_ready[q], static_cast<uint32_t>((seq / kItemRing) & 1), &c->abort, status)) return -1;
+  return *reinterpret_cast<volatile int*>(&c->item[q]);
+}
+
+// Producer side of the dynamic schedule: draw the next tile and announce it as tile `seq` of this CTA.
+template <class Ctrl>
+__device__ __forceinline__ int draw_item(Ctrl* c, int* tile_counter, int seq, int total_items) {
+  int item = atomicAdd(tile_counter, 1);
+  if (item >= total_items) item = -1;
+  const int q = seq % kItemRing;
+  *reinterpret_cast<volatile int*>(&c->item[q]) = item;
+  ptx::mbar_arrive(&c->item_ready[q]);  // release: the item is visible to whoever sees the phase flip
+  return item;
+}
+
+// Waits (bounded) until `done` says that every activated row of an expert is written: `need` arrivals.
+// Returns false when the wait was given up (status and *abort raised) or another role raised *abort.
+__device__ __forceinline__ bool wait_expert_done(const int* done, int need, int* abort, int* status) {
+  const unsigned long long start = ptx::global_timer();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(done) < need) {
+    if ((++spins & 15u) == 0) {
+      if (*reinterpret_cast<volatile int*>(abort)) return false;
+      if (ptx::global_timer() - start > ptx::kWaitLimitNs) {
+        *reinterpret_cast<volatile int*>(abort) = 1;
+        atomicOr(status, B200MOE_STATUS_TIMEOUT);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // One epilogue warp drains its 32 TMEM lanes (= 32 output channels) of one tile:
 // D[channel][row] FP32 -> out[row0 + row][channel] BF16, SwiGLU first when kGateUp
 // (gate columns at taddr, up columns at taddr + token_tile). kSumPair: the tile was accumulated as two partial

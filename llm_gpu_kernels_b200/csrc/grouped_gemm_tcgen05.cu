@@ -55,7 +55,6 @@ constexpr int kMmaWarpB = 6;  // second MMA-issuing warp
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
-constexpr int kItemRing = 16;  // tiles a dynamic producer may announce ahead of the epilogue
 static_assert(kItemRing >= kMaxStages + 3, "producer could lap the item ring");
 
 struct Ctrl {
@@ -71,26 +70,6 @@ struct Ctrl {
   Tables tables;
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
-
-// Acquire load of a completion counter another SM bumps.
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// The tile a role works on next. Static schedule: tile seq of this CTA is blockIdx.x + seq * gridDim.x.
-// Dynamic schedule: the producer draws tiles from a global counter and announces them in a small ring
-// that the MMA thread and the epilogue warps follow; -1 ends the work.
-__device__ __forceinline__ int follow_item(Ctrl* c, bool dynamic, int seq, int total_items, int* status) {
-  if (!dynamic) {
-    const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
-    return item < total_items ? static_cast<int>(item) : -1;
-  }
-  const int q = seq % kItemRing;
-  if (!mbar_wait(&c->item_ready[q], static_cast<uint32_t>((seq / kItemRing) & 1), &c->abort, status)) return -1;
-  return *reinterpret_cast<volatile int*>(&c->item[q]);
-}
 
 // chain_done: per-expert completion counters of the gate/up stage (null = stages separated by kernel
 // boundaries). The gate/up kernel adds one per epilogue warp and tile; the down kernel, given
@@ -165,35 +144,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       bool ok = true;
       int ready_expert = -1;  // activated rows of this expert are known to be complete
       for (int seq = 0; ok; ++seq) {
-        int item;
-        if (dynamic) {
-          item = atomicAdd(tile_counter, 1);
-          if (item >= total_items) item = -1;
-          const int q = seq % kItemRing;
-          *reinterpret_cast<volatile int*>(&c->item[q]) = item;
-          mbar_arrive(&c->item_ready[q]);  // release: the item is visible to whoever sees the phase flip
-        } else {
-          item = follow_item(c, false, seq, total_items, status);
-        }
+        const int item = dynamic ? draw_item(c, tile_counter, seq, total_items)
+                                 : follow_item(c, false, seq, total_items, status);
         if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
         if (chained && t.expert != ready_expert) {
           const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
-          const unsigned long long start = global_timer();
-          uint32_t spins = 0;
-          while (ld_acquire_gpu(chain_done + t.expert) < need) {
-            if ((++spins & 15u) == 0) {
-              if (*reinterpret_cast<volatile int*>(&c->abort)) { ok = false; break; }
-              if (global_timer() - start > kWaitLimitNs) {
-                *reinterpret_cast<volatile int*>(&c->abort) = 1;
-                atomicOr(status, B200MOE_STATUS_TIMEOUT);
-                ok = false;
-                break;
-              }
-            }
-          }
-          if (!ok) break;
+          if (!wait_expert_done(chain_done + t.expert, need, &c->abort, status)) { ok = false; break; }
           ready_expert = t.expert;
         }
         for (int kb = 0; kb < num_kb; ++kb) {

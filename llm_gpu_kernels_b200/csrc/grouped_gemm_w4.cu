@@ -54,6 +54,8 @@ struct Ctrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain[2];
+  uint64_t item_ready[kItemRing];
+  int item[kItemRing];
   uint32_t tmem_base;
   int abort;
   Tables tables;
@@ -85,7 +87,8 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
                        const __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
                        const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
-                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights) {
+                       int w_rows_per_expert, int token_tile, int num_words, int num_operand, int stream_weights,
+                       int* chain_done, int chain_need, int* tile_counter) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -102,7 +105,11 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_launch_dependents();
+  // chain_done / chain_need / tile_counter: the gate/up and down kernels of one forward chained through per-expert
+  // completion counters and a dynamic tile order for down, as in the BF16 kernel (grouped_gemm_tcgen05.cu)
+  const bool chained = !kGateUp && chain_done != nullptr;
+  const bool dynamic = !kGateUp && tile_counter != nullptr;
+  if (!kGateUp) pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_words; ++s) {
       mbar_init(&c->words_full[s], 1);
@@ -118,11 +125,13 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     }
     mbar_init(&c->drain[0], 1);
     mbar_init(&c->drain[1], 1);
+    for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
     c->abort = 0;
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(&c->tmem_base, tmem_cols);
-  pdl_wait();  // the previous kernel's outputs are needed from here on
+  if (!chained) pdl_wait();   // a chained down kernel waits per expert instead (below)
+  if (kGateUp) pdl_launch_dependents();   // after the wait: a dependent then knows the dispatch metadata is complete
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
   tc_fence_before();
   __syncthreads();
@@ -143,7 +152,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       uint32_t pph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      for (int seq = 0; ok; ++seq) {
+        const int item = dynamic ? draw_item(c, tile_counter, seq, total_items)
+                                 : follow_item(c, false, seq, total_items, status);
+        if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
         for (int ws = 0; ws < num_ws; ++ws) {
@@ -173,8 +185,16 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       uint32_t qph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      int ready_expert = -1;   // activated rows of this expert are known to be complete
+      for (int seq = 0; ok; ++seq) {
+        const int item = follow_item(c, dynamic, seq, total_items, status);
+        if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+        if (chained && t.expert != ready_expert) {
+          const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
+          if (!wait_expert_done(chain_done + t.expert, need, &c->abort, status)) { ok = false; break; }
+          ready_expert = t.expert;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&c->op_empty[q], qph ^ 1u, &c->abort, status)) { ok = false; break; }
           mbar_expect_tx(&c->op_full[q], act_bytes);
@@ -196,7 +216,9 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
       int q = 0, acc = 0;
       uint32_t qph = 0, acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      for (int seq = 0; ok; ++seq) {
+        const int item = follow_item(c, dynamic, seq, total_items, status);
+        if (item < 0) { ok = !*reinterpret_cast<volatile int*>(&c->abort); break; }
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const uint32_t idesc = umma_idesc(kTileM, t.n_eff);
         if (!mbar_wait(&c->tmem_empty[acc], acc_phase ^ 1u, &c->abort, status)) { ok = false; break; }
@@ -234,15 +256,25 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     const int quarter = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int seq = 0;; ++seq) {
+      const int item = follow_item(c, dynamic, seq, total_items, status);
+      if (__any_sync(0xffffffffu, item < 0)) break;   // warp-uniform: the TMEM loads below need the whole warp
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       tc_fence_before();
+      if (kGateUp && chain_done != nullptr) {
+        // this lane's rows: ordered for the async proxy (the down kernel reads them by TMA), then visible GPU-wide
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c->tmem_empty[acc]);
+      if (lane == 0) {
+        mbar_arrive(&c->tmem_empty[acc]);
+        if (kGateUp && chain_done != nullptr) atomicAdd(chain_done + t.expert, 1);
+      }
       if (++acc == num_acc) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
@@ -256,7 +288,9 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     int p = 0, q = 0;
     uint32_t pph = 0, qph = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+    for (int seq = 0; ok; ++seq) {
+      const int item = follow_item(c, dynamic, seq, total_items, status);
+      if (__any_sync(0xffffffffu, item < 0)) break;
       const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
       long long srow = static_cast<long long>(t.expert) * w_rows_per_expert + t.ct * kTileM + row +
                        (kGateUp ? half * n_out : 0);
@@ -329,7 +363,7 @@ void rings_for(bool gate_up, int token_tile, int* num_words, int* num_operand, i
 }
 
 template <bool kGateUp>
-cudaError_t launch_w4(const B200MoePlan& p, cudaStream_t s) {
+cudaError_t launch_w4(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
   const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
@@ -345,7 +379,10 @@ cudaError_t launch_w4(const B200MoePlan& p, cudaStream_t s) {
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
       static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
       kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, kGateUp ? p.w4_packed_gate_up : p.w4_packed_down,
-      kGateUp ? p.w4_operand_gate_up : p.w4_operand_down, stream_weights);
+      kGateUp ? p.w4_operand_gate_up : p.w4_operand_down, stream_weights,
+      chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
+      4 * ((sh.intermediate + kTileM - 1) / kTileM),  // epilogue warps x gate/up channel tiles per token tile
+      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr));
   return cudaPeekAtLastError();
 }
 
@@ -369,7 +406,7 @@ int configure_w4(B200MoePlan& p) {
   return B200MOE_OK;
 }
 
-cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s) { return launch_w4<true>(p, s); }
-cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s) { return launch_w4<false>(p, s); }
+cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s, bool chained) { return launch_w4<true>(p, s, chained); }
+cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s, bool chained) { return launch_w4<false>(p, s, chained); }
 
 }  // namespace b200moe

@@ -49,7 +49,6 @@ constexpr int kWordsK = 256;                           // K covered by one words
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
 constexpr uint32_t kWordsTileBytes = kTileM * kWordsK / 2;  // one packed tile of 256 K: 16 KB
 constexpr int kCtrlBytes = 4096;
-constexpr int kItemRing = 16;   // tiles the dynamic schedule may announce ahead of the epilogue (see follow_item)
 
 struct Ctrl {
   uint64_t words_full[kMaxWords];
@@ -84,27 +83,6 @@ __device__ __forceinline__ uint4 dequant_word_t(uint32_t w, __nv_bfloat162 scale
   out.z = __byte_perm(pair[0], pair[1], 0x7632);  // k4 k5
   out.w = __byte_perm(pair[2], pair[3], 0x7632);  // k6 k7
   return out;
-}
-
-// Acquire load of a completion counter another SM bumps.
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// The tile a role works on next. Static schedule: blockIdx.x + seq * gridDim.x. Dynamic schedule (the down kernel
-// chained to a gate/up grid that is still running): the words producer draws tiles from a global counter, so that
-// CTAs that start early do more, and announces them in a small ring every other role follows; -1 ends the work.
-// The producer runs at most the words ring (6 stages) plus the accumulator sets ahead of the epilogue: < 16 tiles.
-__device__ __forceinline__ int follow_item(Ctrl* c, bool dynamic, int seq, int total_items, int* status) {
-  if (!dynamic) {
-    const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
-    return item < total_items ? static_cast<int>(item) : -1;
-  }
-  const int q = seq % kItemRing;
-  if (!mbar_wait(&c->item_ready[q], static_cast<uint32_t>((seq / kItemRing) & 1), &c->abort, status)) return -1;
-  return *reinterpret_cast<volatile int*>(&c->item[q]);
 }
 
 // chain_done / chain_need / tile_counter: as in the BF16 kernel (grouped_gemm_tcgen05.cu). The gate/up kernel adds
@@ -185,16 +163,8 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
       long long issued = 0;
       bool ok = true;
       for (int seq = 0; ok; ++seq) {
-        int item;
-        if (dynamic) {
-          item = atomicAdd(tile_counter, 1);
-          if (item >= total_items) item = -1;
-          const int q = seq % kItemRing;
-          *reinterpret_cast<volatile int*>(&c->item[q]) = item;
-          mbar_arrive(&c->item_ready[q]);  // release: the item is visible to whoever sees the phase flip
-        } else {
-          item = follow_item(c, false, seq, total_items, status);
-        }
+        const int item = dynamic ? draw_item(c, tile_counter, seq, total_items)
+                                 : follow_item(c, false, seq, total_items, status);
         if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
@@ -232,20 +202,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         if (chained && t.expert != ready_expert) {
           const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
-          const unsigned long long start = global_timer();
-          uint32_t spins = 0;
-          while (ld_acquire_gpu(chain_done + t.expert) < need) {
-            if ((++spins & 15u) == 0) {
-              if (*reinterpret_cast<volatile int*>(&c->abort)) { ok = false; break; }
-              if (global_timer() - start > kWaitLimitNs) {
-                *reinterpret_cast<volatile int*>(&c->abort) = 1;
-                atomicOr(status, B200MOE_STATUS_TIMEOUT);
-                ok = false;
-                break;
-              }
-            }
-          }
-          if (!ok) break;
+          if (!wait_expert_done(chain_done + t.expert, need, &c->abort, status)) { ok = false; break; }
           ready_expert = t.expert;
         }
         for (int st = 0; st < num_kb / 2; ++st) {   // one operand stage = 128 K = two 64-K row tiles

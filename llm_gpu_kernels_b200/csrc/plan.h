@@ -54,8 +54,8 @@ cudaError_t launch_down_generic(const B200MoePlan& p, cudaStream_t s);
 // scratch and the down kernel draws tiles from the tile counter there (both zeroed by the dispatch).
 cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained);
-cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s);
-cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s);
+cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s, bool chained);
+cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
