@@ -519,7 +519,7 @@ def main():
                      "frac": head["gate_up_gbs"] / peaks["hbm_gbs"],
                      # dram__bytes_read + write of one gate/up launch from the ncu capture summarised in
                      # profiles/moe_layer_subsystems_qwen_bf16.md (BF16, Qwen shape)
-                     "traffic": {17: 583.1e6, 1024: 844.1e6}.get(args.tokens) if (
+                     "traffic": {17: 583.1e6, 1024: 843.4e6}.get(args.tokens) if (
                          packed is None and args.shape == "qwen" and not args.zipf) else None,
                      "tensor": {"achieved_tflops": head["tflops"], "peak_tflops": peaks["bf16_tflops"],
                                 "frac": head["tensor_frac"]},
