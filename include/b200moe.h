@@ -92,7 +92,8 @@ typedef struct {
   size_t activated;     /* [R,I] bf16 */
   size_t down_output;   /* [R,H] bf16 */
   size_t status;        /* [1] int32 */
-  size_t scratch;       /* dispatch partial histograms */
+  size_t scratch;       /* dispatch partial histograms, router flag, tile counter and per-expert completion
+                           counters of the chained GEMM kernels */
   int32_t token_tile;   /* resolved tile */
   int32_t schedule;     /* resolved schedule */
   int32_t launches;     /* kernels one forward enqueues */
@@ -254,7 +255,7 @@ typedef struct {
   int32_t reserved2;
 } B200MoeEpArgs;
 
-/* The int32 words (inside the bound `scratch` buffer) through which the two BF16 GEMM kernels of one forward
+/* The int32 words (inside the bound `scratch` buffer) through which the two GEMM kernels of one forward
  * synchronise: a tile counter and one completion counter per expert. An ordinary plan's dispatch zeroes
  * them; for external_dispatch = 2 the caller must, before every forward. No reference counterpart. */
 int b200moe_plan_chain(B200MoePlan* plan, void** first_word, int32_t* words);
