@@ -242,10 +242,14 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
 }  // namespace
 
-int router_ksplit(int hidden) {
+int router_ksplit(int hidden, int tokens) {
   const int num_kb = (hidden + kBlockK - 1) / kBlockK;
   int split = 1;
   while (split < 8 && num_kb / (split * 2) >= 2) split *= 2;  // at least two k-blocks per CTA
+  // Only about 16 clusters of 8 CTAs (one CTA per SM) are resident at a time: beyond that the router ran in
+  // waves (13 us at 8 token tiles, 27 us at 17). Smaller clusters keep all token tiles in one wave.
+  const int tiles = (tokens + kTileTokens - 1) / kTileTokens;
+  while (split > 1 && tiles * split > 128) split /= 2;
   return split;
 }
 
@@ -253,7 +257,7 @@ int configure_router_tc(B200MoePlan& p) {
   const int e_pad = (p.shape.experts + 15) / 16 * 16;
   const int stage = kTileTokens * 128 + e_pad * 128;
   const int num_kb = (p.shape.hidden + kBlockK - 1) / kBlockK;
-  const int ksplit = router_ksplit(p.shape.hidden);
+  const int ksplit = router_ksplit(p.shape.hidden, p.shape.tokens);
   const int kb_per = (num_kb + ksplit - 1) / ksplit;
   int stages = (kSmemLimit - kCtrlBytes - 1024) / stage;
   if (stages > kMaxStages) stages = kMaxStages;
