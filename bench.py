@@ -332,10 +332,56 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
     for _ in range(3):
         e2e_step()
     barrier()
-    # one forward in flight per rank: the ranks' kernels wait on one another, so a second forward on a second
-    # stream could meet its peers in a different order on different ranks
     e2e_ms = event_ms(e2e_step, steps, stream)
     torch.cuda.synchronize(dev)
+    extra = []
+    if mode == "peer":
+        # The same with three forwards in flight per rank, as at N=1: two more layers (own activations, workspace
+        # and peer buffers, same weights), each captured as a graph and replayed on a stream of its own. Every rank
+        # issues the three in the same order; the only kernels that wait for other GPUs are one-block barriers, so
+        # forwards of different slots cannot block each other's progress.
+        slots = [{"x": x, "graph": graph, "out": ep.token_plan.output, "x_pinned": x_pinned, "out_pinned": out_pinned,
+                  "stream": torch.cuda.Stream(device=dev)}]
+        weights_dev = (ep.expert_plan.gate_up, ep.expert_plan.down)
+        for _ in range(2):
+            x2, ids2, rw2 = x.clone(), ids.clone(), rw.clone()
+            ep2 = prepare(x2, weights_dev[0], weights_dev[1], ids2, rw2, experts=e, router_weight=wr.to(dev))
+            for _ in range(3):
+                ep2.run()
+            torch.cuda.synchronize(dev)
+            graph2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph2, stream=torch.cuda.Stream(device=dev)):
+                ep2.run()
+            extra.append(ep2)
+            slots.append({"x": x2, "graph": graph2, "out": ep2.token_plan.output,
+                          "x_pinned": x_host.clone().pin_memory(),
+                          "out_pinned": torch.empty(tokens, h, dtype=torch.bfloat16).pin_memory(),
+                          "stream": torch.cuda.Stream(device=dev)})
+
+        def e2e_pipelined(count):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for slot in slots:
+                slot["stream"].wait_event(start)
+            for i in range(count):
+                slot = slots[i % len(slots)]
+                with torch.cuda.stream(slot["stream"]):
+                    slot["x"].copy_(slot["x_pinned"], non_blocking=True)
+                    slot["graph"].replay()
+                    slot["out_pinned"].copy_(slot["out"], non_blocking=True)
+            for slot in slots:
+                stream.wait_stream(slot["stream"])
+            end.record(stream)
+            end.synchronize()
+            return start.elapsed_time(end) / count
+
+        e2e_pipelined(6)
+        barrier()
+        e2e_serial_ms, e2e_ms = e2e_ms, e2e_pipelined(steps)
+        torch.cuda.synchronize(dev)
+        assert all(torch.equal(slot["out_pinned"], out_pinned) for slot in slots[1:]), "the pipeline slots disagree"
+        for status_of in (ep, *extra):
+            status_of.check_inputs()
     if mode == "nccl":
         launches = ep.backend.token_plan.kernel_launches + 1 + ep.backend.expert_plan.kernel_launches
         rows, tile = ep.stats.rows_received, ep.backend.expert_plan.token_tile
@@ -343,9 +389,11 @@ def bench_ep(tokens, weights_cpu, x_host, dev, steps, warmup, rank, world, mode)
         launches = ep.token_plan.kernel_launches + 1 + 1 + 2 + 2 + 2
         rows, tile = ep.rows_received, ep.expert_plan.token_tile
         torch.distributed.barrier()
-        ep.close()
-    return {"ms": ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms, "rows_received": rows, "launches": launches,
-            "token_tile": tile, "timing": timing}
+        for layer in (*extra, ep):
+            layer.close()
+    return {"ms": ms, "ms_eager": eager_ms, "ms_e2e": e2e_ms, "ms_e2e_serial": e2e_serial_ms if extra else e2e_ms,
+            "in_flight": 1 + len(extra), "rows_received": rows, "launches": launches, "token_tile": tile,
+            "timing": timing}
 
 
 def cpu_baseline(tokens, weights_cpu, x_cpu, repeats):
@@ -485,7 +533,10 @@ def main():
                            "rows_received_max": max_rows, "rows_received_mean": mean_rows},
                 "e2e": {"value": world * args.tokens / (e2e_ms * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": args.tokens * QWEN["hidden"] * 2,
-                        "d2h_bytes_per_step": args.tokens * QWEN["hidden"] * 2, "ms_per_step": e2e_ms},
+                        "d2h_bytes_per_step": args.tokens * QWEN["hidden"] * 2, "ms_per_step": e2e_ms,
+                        "ms_per_step_one_in_flight_rank0": ep["ms_e2e_serial"],
+                        "mode": f"{ep['in_flight']} forward(s) in flight per rank, each step copies its input from pinned "
+                                "host memory and its BF16 result back; max over ranks"},
                 "gpu_launches": args.steps * ep["launches"],
                 "clocks": clocks.summary(),
                 "roofline": {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
