@@ -334,8 +334,9 @@ class PeerExpertParallelMoE:
         tp.dispatch()
         check(lib.b200moe_ep_exchange_counts(args, stream))
         check(lib.b200moe_ep_send_rows(args, stream))
-        ep.launches[2].run()   # gate/up + SwiGLU over the received rows
-        ep.launches[3].run()   # down
+        # gate/up + SwiGLU and down over the received rows, as one forward of the expert plan: the two kernels are
+        # then chained through the completion counters that the count exchange zeroed
+        check(ep._forward(ep._plan, stream))
         check(lib.b200moe_ep_return_rows(args, stream))
         tp.combine()
         return tp.output
