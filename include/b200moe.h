@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 /* error codes */
 #define B200MOE_OK 0
@@ -74,7 +74,9 @@ typedef struct {
                              chained through them as in an ordinary plan */
   int32_t router_bf16_weights; /* 1: the router rounds its renormalised weights through BF16, as the model the
                              reference captured does (scripts/capture_qwen3_moe_layer0.py:587-588) */
-  int32_t reserved[2];
+  int32_t unchained;      /* 1: b200moe_forward separates gate/up and down by an ordinary kernel boundary instead of
+                             chaining them through the per-expert completion counters (for A/B timing) */
+  int32_t reserved[1];
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned
@@ -253,6 +255,8 @@ typedef struct {
   void* expert_chain;
   int32_t expert_chain_words;
   int32_t reserved2;
+  void* expert_status;            /* [1] int32 status word of the expert plan, restarted by the count exchange every
+                                     forward (that plan has no dispatch of its own to do it); may be NULL */
 } B200MoeEpArgs;
 
 /* The int32 words (inside the bound `scratch` buffer) through which the two GEMM kernels of one forward

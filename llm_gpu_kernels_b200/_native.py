@@ -10,7 +10,7 @@ import threading
 from pathlib import Path
 
 LIBRARY_PATH = Path(__file__).resolve().parent / "libb200moe.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 STATUS_BAD_ID = 1
 STATUS_BAD_WEIGHT = 2
@@ -31,8 +31,8 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_STATE = -1, -2, -3, -4
 class Shape(ctypes.Structure):
     _fields_ = [(name, ctypes.c_int32) for name in (
         "tokens", "experts", "topk", "hidden", "intermediate", "ids_are_int64", "gate_up_format",
-        "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch", "router_bf16_weights")] + [
-        ("reserved", ctypes.c_int32 * 2)]
+        "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch", "router_bf16_weights",
+        "unchained")] + [("reserved", ctypes.c_int32 * 1)]
 
 
 WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "ranks",
@@ -74,7 +74,8 @@ class EpArgs(ctypes.Structure):
             "x", "ids", "ranks", "counts", "expert_counts", "expert_offsets", "expert_tasks", "expert_rows",
             "expert_output", "tables", "status")] + [(name, ctypes.c_void_p * EP_MAX_RANKS) for name in (
                 "recv_rows_peers", "return_rows_peers", "all_counts_peers", "flags_peers")] + [
-        ("expert_chain", ctypes.c_void_p), ("expert_chain_words", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
+        ("expert_chain", ctypes.c_void_p), ("expert_chain_words", ctypes.c_int32), ("reserved2", ctypes.c_int32),
+        ("expert_status", ctypes.c_void_p)]
 
 
 EXPORTS = {

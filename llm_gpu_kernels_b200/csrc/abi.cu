@@ -2,7 +2,6 @@
 // descriptor encoding, and the launch sequence. See include/b200moe.h.
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <new>
 #include "plan.h"
@@ -296,6 +295,10 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
       for (const Named& n : own_dispatch)
         if (!check(n)) return B200MOE_ERR_INVALID;
     if (s.route_only != 2 && !check({b->grouped_input, "grouped_input"})) return B200MOE_ERR_INVALID;
+    if (!s.external_dispatch && s.ids_are_int64 && reinterpret_cast<uintptr_t>(b->ids) % 8) {
+      set_error("buffer 'ids' (int64) is not 8-byte aligned");
+      return B200MOE_ERR_INVALID;
+    }
     if (s.use_router && !b->router_weight) {
       set_error("use_router is set but router_weight is null");
       return B200MOE_ERR_INVALID;
@@ -320,9 +323,8 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     if ((rc = configure_router_tc(*p))) return rc;
     p->router_tc = true;
   } else if (s.tokens > 0 && s.use_router) {
-    const size_t smem = router_smem_bytes(s.hidden, s.experts);
-    if (smem > 48 * 1024) {
-      rc = check_cuda(router_opt_in_smem(smem), "router shared-memory opt-in");
+    if (router_smem_bytes(s.hidden, s.experts) > 48 * 1024) {
+      rc = check_cuda(router_opt_in_smem(), "router shared-memory opt-in");
       if (rc) return rc;
     }
   }
@@ -384,8 +386,8 @@ int b200moe_dispatch(B200MoePlan* p, void* stream) {
 // Inside b200moe_forward the two BF16 tensor-core GEMMs are chained through per-expert counters.
 static bool w4_in_tmem(const B200MoePlan* p) { return p->token_tile <= 64; }
 static bool chain_stages(const B200MoePlan* p) {
-  static const bool off = std::getenv("B200MOE_NO_CHAIN") != nullptr;
-  if (off || p->schedule != B200MOE_SCHEDULE_TCGEN05 || p->shape.external_dispatch == 1 || !p->buf.scratch) return false;
+  if (p->shape.unchained || p->schedule != B200MOE_SCHEDULE_TCGEN05 || p->shape.external_dispatch == 1 || !p->buf.scratch)
+    return false;
   const bool g4 = is_w4(p->shape.gate_up_format), d4 = is_w4(p->shape.down_format);
   return g4 == d4;   // both stages BF16 or both W4 (the two W4 variants are chosen by token tile, the same for both)
 }
@@ -442,8 +444,10 @@ int b200moe_combine(B200MoePlan* p, void* stream) {
 int b200moe_forward(B200MoePlan* p, void* stream) {
   int rc;
   if (p && p->bound && p->shape.external_dispatch) {
-    if ((rc = b200moe_gate_up(p, stream))) return rc;
-    return b200moe_down(p, stream);
+    // external_dispatch = 2: whoever wrote the metadata zeroed the chain words, so the two GEMMs chain
+    const bool chained = chain_stages(p);
+    if ((rc = gate_up_stage(p, stream, chained))) return rc;
+    return down_stage(p, stream, chained);
   }
   if ((rc = b200moe_router(p, stream))) return rc;
   if ((rc = b200moe_dispatch(p, stream))) return rc;

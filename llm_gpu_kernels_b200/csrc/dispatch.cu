@@ -445,6 +445,17 @@ extern "C" int b200moe_dispatch_static(const B200MoeDispatchArgs* a, void* cuda_
       set_error("static dispatch: null buffer");
       return B200MOE_ERR_INVALID;
     }
+  // a misaligned pointer from a C caller must come back as an error, not as a device fault
+  const uintptr_t ids_align = a->ids_are_int64 ? 8 : 4;
+  const void* words4[] = {a->routing_weights, a->counts, a->offsets, a->cursors, a->tasks, a->ranks, a->mapping,
+                          a->status};
+  bool aligned = reinterpret_cast<uintptr_t>(a->ids) % ids_align == 0 &&
+                 (reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->grouped_input)) % 2 == 0;
+  for (const void* ptr : words4) aligned = aligned && reinterpret_cast<uintptr_t>(ptr) % 4 == 0;
+  if (!aligned) {
+    set_error("static dispatch: misaligned buffer (int32 / float32 buffers 4 bytes, int64 ids 8 bytes, BF16 rows 2 bytes)");
+    return B200MOE_ERR_INVALID;
+  }
   int* scratch = nullptr;
   int rc = static_scratch_for_current_device(&scratch);
   if (rc) return rc;

@@ -79,6 +79,9 @@ ep_counts_kernel(const B200MoeEpArgs a) {
   const int* counts = static_cast<const int*>(a.counts);
   // the expert plan's GEMM kernels synchronise through these words and expect them zero at their start
   for (int i = tid; i < a.expert_chain_words; i += blockDim.x) static_cast<int*>(a.expert_chain)[i] = 0;
+  // that plan has no dispatch of its own, so its status word restarts here (the previous forward is complete:
+  // this kernel runs behind it on the stream)
+  if (tid == 0 && a.expert_status) *static_cast<int*>(a.expert_status) = 0;
   if (tid < E) {
     const int c = counts[tid];
     for (int g = 0; g < G; ++g) static_cast<int*>(a.all_counts_peers[g])[a.rank * E + tid] = c;
@@ -116,8 +119,11 @@ ep_counts_kernel(const B200MoeEpArgs a) {
     for (int s = 0; s < a.rank; ++s) before += A[s * E + tid];
     send_base[tid] = owner_prefix[tid] + before;  // where my first row of expert `tid` lands on its owner
   }
-  // more rows than the receive buffer holds: run no expert tile at all and say so
-  const bool overflow = owner_prefix[lo + El - 1] + colsum[lo + El - 1] > a.capacity;
+  // More rows for some owner than its receive buffer holds: every rank sees the same [G][E] matrix, so every rank
+  // takes the same decision - no expert tile runs anywhere and every rank's status says so (a sender whose own
+  // rows all fit would otherwise combine rows that the overflowing owner never produced).
+  bool overflow = false;
+  for (int g = 0; g < G; ++g) overflow |= owner_prefix[g * El + El - 1] + colsum[g * El + El - 1] > a.capacity;
   if (overflow && tid == 0) atomicOr(static_cast<int*>(a.status), B200MOE_STATUS_EP_OVERFLOW);
   if (tid < El) {
     const int e = lo + tid;

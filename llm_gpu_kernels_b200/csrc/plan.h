@@ -61,7 +61,7 @@ cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
 
 size_t router_smem_bytes(int hidden, int experts);
-cudaError_t router_opt_in_smem(size_t bytes);
+cudaError_t router_opt_in_smem();
 
 // One-time per-plan set-up of the tcgen05 kernels (smem opt-in, stage counts).
 int configure_tc(B200MoePlan& p);

@@ -148,12 +148,13 @@ size_t router_smem_bytes(int hidden, int experts) {
   return (static_cast<size_t>(kRouterTokens) * hidden + kRouterTokens * experts) * sizeof(float);
 }
 
-cudaError_t router_opt_in_smem(size_t bytes) {
-  cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(bytes));
+// The opt-in is an attribute of the kernel, not of a plan: always raise it to the device limit, so that binding a
+// second plan with a smaller hidden size cannot lower it under the first plan's launches.
+cudaError_t router_opt_in_smem() {
+  constexpr int kLimit = 227 * 1024;
+  cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLimit);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(router_topk_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(bytes));
+  return cudaFuncSetAttribute(router_topk_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLimit);
 }
 
 }  // namespace b200moe

@@ -294,7 +294,7 @@ cudaError_t launch_router_typed(const B200MoePlan& p, cudaStream_t s, IdT* ids) 
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = 2;
   int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
   return cudaLaunchKernelEx(&cfg, router_tc_kernel<IdT>, p.tm_x, p.tm_router_w, ids,
                             static_cast<float*>(p.buf.routing_weights), status, sh.tokens, sh.experts, sh.hidden,

@@ -210,7 +210,7 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
              route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None,
-             router_bf16_weights=False, residual=None):
+             router_bf16_weights=False, residual=None, unchained=False):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
@@ -236,7 +236,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
                           use_router=int(router_weight is not None),
                           route_only=0 if route_only_experts is None else (1 if copy_rows else 2),
-                          router_bf16_weights=int(bool(router_bf16_weights)))
+                          router_bf16_weights=int(bool(router_bf16_weights)), unchained=int(bool(unchained)))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:

@@ -315,7 +315,8 @@ class PeerExpertParallelMoE:
                               expert_counts=ptr(ep.counts), expert_offsets=ptr(ep.offsets), expert_tasks=ptr(ep.tasks),
                               expert_rows=ptr(self.expert_rows), expert_output=ptr(ep.down_output),
                               tables=ptr(self.tables), status=ptr(tp.status),
-                              expert_chain=ctypes.c_void_p(ep.chain[0]), expert_chain_words=ep.chain[1])
+                              expert_chain=ctypes.c_void_p(ep.chain[0]), expert_chain_words=ep.chain[1],
+                              expert_status=ptr(ep.status))
         for field, name in (("recv_rows_peers", "recv"), ("return_rows_peers", "ret"),
                             ("all_counts_peers", "counts"), ("flags_peers", "flags")):
             array = getattr(args, field)

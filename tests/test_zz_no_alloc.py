@@ -6,7 +6,8 @@ is handed only its input and output buffers. For them the library keeps the
 scratch of the dispatch kernels in a fixed device array of its own, good for
 up to 65536 routes. These tests call that entry point through the C ABI and
 compare it, bit for bit (the tolerance of every dispatch test here), with the
-regular ``b200moe_dispatch`` that works on a caller-allocated workspace.
+regular ``b200moe_dispatch`` that works on a caller-allocated workspace, and with
+the CPU dispatch oracle.
 Collected last on purpose: a run that stops at the first failure has then
 already run every other test.
 """
@@ -16,6 +17,7 @@ import pytest
 import torch
 
 from llm_gpu_kernels_b200 import _native
+from oracle import moe_oracle as O
 from tests.util import make_inputs
 
 
@@ -36,6 +38,17 @@ def test_static_dispatch_refuses_sizes_beyond_its_scratch():
         fields = dict(tokens=4, experts=8, topk=2, hidden=64, token_tile=16)
         fields.update(bad)
         assert lib.b200moe_dispatch_static(ctypes.byref(_native.DispatchArgs(**fields)), None) == _native.ERR_INVALID
+    # misaligned pointers are refused on the host too (never dereferenced: the check comes before any launch)
+    names = ("x", "ids", "routing_weights", "counts", "offsets", "cursors", "tasks", "ranks", "mapping",
+             "grouped_input", "status")
+    good = {name: 0x10000 + 0x1000 * i for i, name in enumerate(names)}
+    for name, skew, int64 in (("counts", 2, 0), ("routing_weights", 1, 0), ("ids", 4, 1), ("ids", 2, 0), ("x", 1, 0),
+                              ("status", 2, 0), ("mapping", 3, 0)):
+        ptrs = dict(good)
+        ptrs[name] += skew
+        bad = _native.DispatchArgs(tokens=4, experts=8, topk=2, hidden=64, ids_are_int64=int64, token_tile=16, **ptrs)
+        assert lib.b200moe_dispatch_static(ctypes.byref(bad), None) == _native.ERR_INVALID, name
+        assert "misaligned" in _native.last_error()
 
 
 @pytest.mark.gpu
@@ -77,3 +90,10 @@ def test_static_dispatch_matches_regular_dispatch_twice(tokens, experts, topk, h
             else:
                 assert torch.equal(mine, theirs), f"call {call}: {name}"
         assert int(out["status"].item()) == (0 if call == 0 else 3)
+        # and against the CPU oracle directly (an invalid id has rank / mapping -1 there as well)
+        counts, offsets, ranks, mapping = O.dispatch_oracle(ids.cpu(), experts)
+        for name, want in (("counts", counts), ("offsets", offsets), ("ranks", ranks), ("mapping", mapping)):
+            assert torch.equal(out[name].cpu(), want), f"call {call}: {name} against the oracle"
+        valid = mapping >= 0
+        gathered = out["grouped_input"].cpu()[mapping[valid].long()]
+        assert torch.equal(gathered, x.cpu().repeat_interleave(topk, 0)[valid]), f"call {call}: rows against the oracle"
