@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from . import _native
+from . import _native, _ops
 from .gemm import GemmConfig
 
 STAGE_NAMES = ("router", "dispatch", "gate_up_swiglu", "down", "combine")
@@ -92,6 +92,7 @@ class PreparedMoE:
     chain: tuple = None       # expert-side plans: (device address, count) of the int32 words the exchange zeroes
     _plan: object = field(default=None, repr=False)
     _forward: object = field(default=None, repr=False)
+    _op_args: tuple = field(default=None, repr=False)
 
     @property
     def workspace_bytes(self):
@@ -131,14 +132,18 @@ class PreparedMoE:
         self._stage(4)
 
     def run(self):
+        """One forward on the current stream, through the registered PyTorch operator
+        ``torch.ops.b200moe.forward`` (a thin wrapper of ``b200moe_forward``), so that graph capture and
+        ``torch.compile`` see which tensors the call writes."""
         if self.x.shape[0] == 0:
             return self.output
-        device = self.x.device
-        if torch.cuda.current_device() == device.index:
-            _native.check(self._forward(self._plan, torch.cuda.current_stream(device).cuda_stream))
-        else:
-            with torch.cuda.device(device):
-                _native.check(self._forward(self._plan, torch.cuda.current_stream(device).cuda_stream))
+        if self._op_args is None:
+            weights = [t for t in (self.gate_up, self.down, self.router_weight, self.gate_up_scales,
+                                   self.down_scales, self.valid_routes, self.residual) if t is not None]
+            workspace = [self.counts, self.offsets, self.cursors, self.tasks, self.mapping, self.ranks,
+                         self.grouped_input, self.activated, self.down_output, self.status, self.scratch]
+            self._op_args = (self._plan.value, self.x, weights, self.ids, self.routing_weights, self.output, workspace)
+        _ops.forward(*self._op_args)
         return self.output
 
     def __del__(self):

@@ -102,6 +102,55 @@ def test_two_rank_expert_parallel(shape):
     assert sum(v[1] for v in result.values()) == 2 * shape[0] * shape[2]
 
 
+def _run_overflow(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from llm_gpu_kernels_b200.moe_ep import expert_range, prepare_peer_ep_moe
+        t_local, experts, topk, hidden, inter = 40, 8, 2, 128, 64
+        x, gate_up, down, ids_all, rw_all = make_inputs(t_local * world, experts, topk, hidden, inter, seed=12,
+                                                        pattern="balanced", wscale=0.1)
+        lo, hi = expert_range(rank, world, experts)
+        mine = slice(rank * t_local, (rank + 1) * t_local)
+        ids, rw = ids_all[mine].contiguous().to(dev), rw_all[mine].contiguous().to(dev)
+        capacity = 100                      # balanced routes: 80 rows per rank fit; everything to one expert does not
+        peer = prepare_peer_ep_moe(x[mine].contiguous().to(dev), gate_up[lo:hi].contiguous().to(dev),
+                                   down[lo:hi].contiguous().to(dev), ids, rw, experts=experts, capacity=capacity)
+        try:
+            out = peer.run().clone()
+            torch.cuda.synchronize()
+            peer.check_inputs()
+            ref = O.moe_oracle(x[mine], gate_up, down, ids.cpu(), rw.cpu())
+            assert O.error_metrics(out.float().cpu(), ref)["relative_rms"] <= 5e-3
+            keep = ids.clone()
+            ids.fill_(experts - 1)          # 160 rows for the last rank: more than its receive buffer holds
+            peer.run()
+            torch.cuda.synchronize()
+            status = int(peer.token_plan.status.item())
+            with pytest.raises(ValueError, match="status=8"):
+                peer.check_inputs()
+            ids.copy_(keep)                 # the next forward restarts the status words on both plans
+            assert torch.equal(peer.run(), out)
+            peer.check_inputs()
+            result[rank] = status
+        finally:
+            peer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_receive_overflow_is_flagged_on_every_rank():
+    """Every rank sees the same count matrix, so the rank whose own rows all fit must raise status 8 too (it
+    would otherwise combine rows the overflowing owner never produced)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    result = mp.Manager().dict()
+    mp.spawn(_run_overflow, args=(2, 29747, result), nprocs=2, join=True)
+    assert dict(result) == {0: 8, 1: 8}
+
+
 def test_absent_peer_is_reported_not_waited_for():
     """A rank whose peer never arrives: the count exchange's barrier gives up after its 1 s bound, raises status
     bit 4 (a bounded wait ran out) and returns; the context stays usable. The "peer" is a second set of local

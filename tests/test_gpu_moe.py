@@ -383,3 +383,35 @@ def test_bind_rejects_bad_arguments(dev):
         prepare_moe(x, gu, dn, ids, rw, router_weight=torch.zeros(3, 128, device=dev, dtype=torch.bfloat16))
     with pytest.raises(RuntimeError):
         prepare_moe(*make_inputs(4, 4, 2, 67, 33, device=dev), schedule="tcgen05")
+
+
+def test_registered_operator_graph_capture_and_compile(dev):
+    """``run()`` goes through ``torch.ops.b200moe.forward``: the op passes PyTorch's schema / fake-tensor checks,
+    is captured by ``torch.cuda.graph`` and traces under ``torch.compile(fullgraph=True)`` without a graph break."""
+    import llm_gpu_kernels_b200._ops  # noqa: F401  (registers the op)
+    cpu = make_inputs(48, 8, 2, 256, 128, seed=61, wscale=0.1)
+    gpu = tuple(a.to(dev) for a in cpu)
+    p = prep()(*gpu)
+    base = p.base
+    want = p.run().clone()
+    check_output(want, cpu)
+    args = base._op_args
+    assert args is not None and args[0] == base._plan.value
+    torch.library.opcheck(torch.ops.b200moe.forward.default, args, test_utils=("test_schema", "test_faketensor"))
+    base.output.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=torch.cuda.Stream(device=dev)):
+        torch.ops.b200moe.forward(*args)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(base.output, want)
+
+    def layer(scale):
+        torch.ops.b200moe.forward(*args)
+        return base.output.float() * scale
+
+    base.output.zero_()
+    compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")
+    got = compiled(torch.tensor(2.0, device=dev))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want.float() * 2.0)

@@ -59,3 +59,19 @@ def seeded_layer(seed, tokens, hidden, inter, experts, wscale=0.02, device="cpu"
     down = (wscale * torch.randn(experts, hidden, inter, generator=g)).bfloat16()
     x = torch.randn(tokens, hidden, generator=g).bfloat16()
     return tuple(t.to(device) for t in (wr, gate_up, down, x))
+
+
+def zipf_bias(experts, s, seed=0):
+    """log pmf of a Zipf(s) popularity over a seeded random permutation of the experts."""
+    g = torch.Generator().manual_seed(seed)
+    pmf = torch.arange(1, experts + 1, dtype=torch.float64) ** (-s)
+    pmf = (pmf / pmf.sum())[torch.randperm(experts, generator=g)]
+    return pmf.log().float()
+
+
+def zipf_routes(x, router_weight, topk, s, seed=0):
+    """Skewed routing stress: softmax top-k with renormalisation over router logits plus a Zipf(s)
+    popularity prior (computed on the host: the device router has no bias input). Returns (ids int32, weights)."""
+    logits = x.float() @ router_weight.float().T + zipf_bias(router_weight.shape[0], s, seed)
+    weights, ids = torch.topk(torch.softmax(logits, dim=1), topk, dim=-1)
+    return ids.to(torch.int32), (weights / weights.sum(-1, keepdim=True)).float()
