@@ -31,6 +31,31 @@ SCHEMA = "llm_gpu_kernels.moe_real_trace"
 SCHEMA_VERSION = 1
 TRACE_TENSOR_NAMES = ("x", "expert_ids", "route_weights")
 QWEN3_30B_A3B = dict(experts=128, hidden=2048, intermediate=768, topk=8)
+# identity of the capture the reference pins (reference moe_real_trace.py:22-23); other captures pass their own
+MODEL_REPO_ID = "Qwen/Qwen3-30B-A3B"
+MODEL_REVISION = "ad44e777bcd18fa416d9da3bd8f70d33ebb85d39"
+# what a stored route weight means (reference moe_real_trace.py:377-383): the model's BF16 router output,
+# promoted exactly to FP32, not renormalised, ids unique per token
+ROUTING_CONTRACT = {"source_dtype": "bfloat16", "stored_dtype": "float32",
+                    "conversion": "exact_bfloat16_to_float32_promotion", "renormalization": "none",
+                    "unique_expert_ids_per_token": True}
+TRACE_FORMAT = "torch_weights_only_tensor_dict"
+WEIGHTS_FORMAT = "torch_weights_only_bundle"
+
+
+def _model_block(dims, repo_id, revision):
+    return {"repo_id": repo_id, "revision": revision, "num_experts": dims["experts"], "hidden_size": dims["hidden"],
+            "intermediate_size": dims["intermediate"], "top_k": dims["topk"]}
+
+
+def _dims_of(model):
+    keys = ("num_experts", "hidden_size", "intermediate_size", "top_k")
+    if (not isinstance(model, dict) or not isinstance(model.get("repo_id"), str)
+            or not isinstance(model.get("revision"), str)
+            or any(type(model.get(k)) is not int or model[k] <= 0 for k in keys)):
+        raise ValueError("manifest model block must name repo_id, revision and positive integer dimensions")
+    return dict(experts=model["num_experts"], hidden=model["hidden_size"],
+                intermediate=model["intermediate_size"], topk=model["top_k"])
 
 
 @dataclass(frozen=True)
@@ -69,7 +94,7 @@ def _sha(value, label):
     return value.lower()
 
 
-def _local_path(value, base_dir: Path, label: str) -> Path:
+def _local_path(value, base_dir: Path, label: str, must_exist: bool = True) -> Path:
     if not isinstance(value, (str, os.PathLike)):
         raise TypeError(f"{label} must be a local filesystem path")
     text = os.fspath(value)
@@ -77,7 +102,7 @@ def _local_path(value, base_dir: Path, label: str) -> Path:
         raise ValueError(f"{label} must be a local path, not a URL")
     path = Path(text)
     path = (base_dir / path if not path.is_absolute() else path).resolve()
-    if not path.is_file():
+    if must_exist and not path.is_file():
         raise ValueError(f"{label} does not name an existing file: {path}")
     if path.suffix.lower() != ".pt":
         raise ValueError(f"{label} must be a local .pt weights-only bundle")
@@ -134,8 +159,17 @@ def validate_weight_tensors(weights, *, dims=QWEN3_30B_A3B):
 
 
 def write_real_moe_trace(directory, x, expert_ids, route_weights, gate_up, down, *, name="trace",
-                         dims=QWEN3_30B_A3B) -> Path:
-    """Write a trace bundle, a shared weight bundle and the manifest; returns the manifest path."""
+                         dims=QWEN3_30B_A3B, provenance=None, repo_id=MODEL_REPO_ID, revision=MODEL_REVISION,
+                         source_manifest_sha256=None) -> Path:
+    """Write a trace bundle, a shared weight bundle and the manifest; returns the manifest path.
+
+    The manifest has the fields of the reference's writer (moe_real_trace.py:314-352): ``status``, the ``model``
+    block, the routing contract, per-tensor records, weight records with ``format`` / ``tensor_name`` /
+    ``source_manifest_sha256``, and ``capture`` (``provenance``, any JSON mapping). With the default dimensions
+    and model identity the reference's own ``validate_real_moe_trace`` accepts it."""
+    if provenance is not None and not isinstance(provenance, dict):
+        raise TypeError("provenance must be a JSON-safe mapping")
+    capture = json.loads(json.dumps(dict(provenance or {}), allow_nan=False))
     directory = Path(directory)
     directory.mkdir(parents=True, exist_ok=True)
     tensors = validate_trace_tensors(x, expert_ids, route_weights, dims=dims)
@@ -144,39 +178,100 @@ def write_real_moe_trace(directory, x, expert_ids, route_weights, gate_up, down,
     torch.save(tensors, trace_path)
     torch.save({k: v.contiguous() for k, v in weights.items()}, weight_path)
     weight_sha = sha256_file(weight_path)
+    source_sha = _sha(source_manifest_sha256 or weight_sha, "source_manifest_sha256")
     manifest = {
-        "schema": SCHEMA, "schema_version": SCHEMA_VERSION, "dims": dict(dims),
-        "trace": {"path": trace_path.name, "sha256": sha256_file(trace_path),
+        "schema": SCHEMA, "schema_version": SCHEMA_VERSION, "status": "passed",
+        "model": _model_block(dims, repo_id, revision), "routing_contract": dict(ROUTING_CONTRACT),
+        "trace": {"path": trace_path.name, "sha256": sha256_file(trace_path), "format": TRACE_FORMAT,
                   "tensors": {k: {"shape": list(v.shape), "dtype": str(v.dtype).removeprefix("torch."),
                                   "sha256": tensor_sha256(v)} for k, v in tensors.items()}},
-        "weights": {k: {"path": weight_path.name, "sha256": weight_sha, "tensor_name": k,
-                        "shape": list(v.shape), "dtype": "bfloat16"} for k, v in weights.items()},
+        "weights": {k: {"path": weight_path.name, "sha256": weight_sha, "format": WEIGHTS_FORMAT, "tensor_name": k,
+                        "shape": list(v.shape), "dtype": "bfloat16", "source_manifest_sha256": source_sha}
+                    for k, v in weights.items()},
+        "capture": capture,
     }
     manifest_path = directory / f"{name}.json"
     partial = manifest_path.with_suffix(".json.partial")
-    partial.write_text(json.dumps(manifest, indent=1), encoding="utf-8")
+    partial.write_text(json.dumps(manifest, indent=2, sort_keys=True, allow_nan=False) + "\n", encoding="utf-8")
     os.replace(partial, manifest_path)   # never a half-written manifest
     return manifest_path
 
 
-def validate_real_moe_trace(manifest_path, *, verify_hashes=True, load_trace=True, load_weights=False,
-                            dims=None) -> RealMoETrace:
-    """Validate a manifest and optionally load its CPU tensors (``weights_only=True`` loads only)."""
-    target = Path(manifest_path).expanduser().resolve(strict=True)
-    manifest = json.loads(target.read_text(encoding="utf-8"))
+def _validate_manifest(manifest, dims):
+    """The manifest rules of the reference (moe_real_trace.py:357-445), with the dimensions taken from the
+    manifest's own ``model`` block instead of being fixed to one model. Returns the dimensions."""
     if not isinstance(manifest, dict) or manifest.get("schema") != SCHEMA or manifest.get("schema_version") != 1:
         raise ValueError("not a moe_real_trace manifest of schema version 1")
-    dims = dims or manifest.get("dims") or QWEN3_30B_A3B
+    if manifest.get("status") != "passed":
+        raise ValueError("real-MoE trace manifest is not marked passed")
+    found = _dims_of(manifest.get("model"))
+    if dims is not None and dict(dims) != found:
+        raise ValueError(f"manifest describes {found}, expected {dict(dims)}")
+    dims = found
+    if manifest.get("routing_contract") != ROUTING_CONTRACT:
+        raise ValueError("manifest routing contract differs from the fixed trace contract")
+    if not isinstance(manifest.get("capture"), dict):
+        raise ValueError("manifest capture metadata must be a JSON object")
     trace, weights = manifest.get("trace"), manifest.get("weights")
     if not isinstance(trace, dict) or not isinstance(weights, dict) or set(weights) != {"gate_up", "down"}:
         raise ValueError("manifest needs a trace record and gate_up / down weight records")
-    if set(trace.get("tensors", {})) != set(TRACE_TENSOR_NAMES):
+    if trace.get("format") != TRACE_FORMAT:
+        raise ValueError("trace bundle format must be weights-only tensor dictionary")
+    _sha(trace.get("sha256"), "trace.sha256")
+    tensors = trace.get("tensors")
+    if not isinstance(tensors, dict) or set(tensors) != set(TRACE_TENSOR_NAMES):
         raise ValueError("trace record must describe x, expert_ids and route_weights")
+    token_counts = set()
+    for name, rec in tensors.items():
+        shape = rec.get("shape") if isinstance(rec, dict) else None
+        if not isinstance(shape, list) or len(shape) != 2 or any(type(v) is not int for v in shape) or shape[0] <= 0:
+            raise ValueError(f"trace.tensors.{name}.shape must be [T, n] with T > 0")
+        _sha(rec.get("sha256"), f"trace.tensors.{name}.sha256")
+        if shape[1] != (dims["hidden"] if name == "x" else dims["topk"]):
+            raise ValueError(f"manifest {name} shape is incompatible with the model dimensions")
+        allowed = {"x": ("bfloat16",), "expert_ids": ("int32", "int64"), "route_weights": ("float32",)}[name]
+        if rec.get("dtype") not in allowed:
+            raise ValueError(f"manifest {name} dtype must be one of {allowed}")
+        token_counts.add(shape[0])
+    if len(token_counts) != 1:
+        raise ValueError("all manifest trace tensors must have the same token count T")
+    shapes = {"gate_up": [dims["experts"], 2 * dims["intermediate"], dims["hidden"]],
+              "down": [dims["experts"], dims["hidden"], dims["intermediate"]]}
+    sources = set()
+    for name, rec in weights.items():
+        if not isinstance(rec, dict) or rec.get("format") != WEIGHTS_FORMAT or rec.get("tensor_name") != name:
+            raise ValueError(f"manifest weights.{name} must declare a weights-only torch bundle holding {name!r}")
+        if rec.get("shape") != shapes[name] or rec.get("dtype") != "bfloat16":
+            raise ValueError(f"manifest weights.{name} shape/dtype violate the model dimensions")
+        sources.add(_sha(rec.get("source_manifest_sha256"), f"weights.{name}.source_manifest_sha256"))
+        _sha(rec.get("sha256"), f"weights.{name}.sha256")
+    if len(sources) != 1:
+        raise ValueError("gate_up and down must cite the same layer-extraction manifest")
     if (weights["gate_up"].get("path") != weights["down"].get("path")
             or weights["gate_up"].get("sha256") != weights["down"].get("sha256")):
         raise ValueError("gate_up and down must reference the same shared weight bundle")
+    return dims
+
+
+def validate_real_moe_trace(manifest_path, *, verify_hashes=True, load_trace=True, load_weights=False,
+                            dims=None, check_weight_files=True) -> RealMoETrace:
+    """Validate a manifest and optionally load its CPU tensors (``weights_only=True`` loads only).
+
+    ``check_weight_files=False`` validates the weight records as written but does not require the (large)
+    weight bundle to be present: for looking at a trace whose weights live elsewhere."""
+    target = Path(manifest_path).expanduser().resolve(strict=True)
+    manifest = json.loads(target.read_text(encoding="utf-8"))
+    dims = _validate_manifest(manifest, dims)
+    trace, weights = manifest["trace"], manifest["weights"]
+    if load_weights and not check_weight_files:
+        raise ValueError("load_weights needs the weight bundle: check_weight_files must stay True")
     base = target.parent
-    records = {"trace": trace, "weights.gate_up": weights["gate_up"], "weights.down": weights["down"]}
+    records = {"trace": trace}
+    if check_weight_files:
+        records.update({"weights.gate_up": weights["gate_up"], "weights.down": weights["down"]})
+    else:
+        for key in ("gate_up", "down"):
+            _local_path(weights[key].get("path"), base, f"weights.{key}.path", must_exist=False)
     paths = {key: _local_path(rec.get("path"), base, f"{key}.path") for key, rec in records.items()}
     if verify_hashes:
         cache = {}

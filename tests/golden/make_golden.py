@@ -9,7 +9,8 @@ It imports the reference's own Python functions - ``moe_reference``
 (src/llm_gpu_kernels/reference.py:17), ``quantize_gate_up`` /
 ``dequantize_gate_up_reference`` (moe_weight_quant.py:35,55),
 ``repack_gate_up`` / ``restore_v1_layout`` (moe_weight_layout.py:81,130),
-``validate_dispatch`` (moe_benchmark.py:139), ``error`` (benchmark.py:28) -
+``validate_dispatch`` (moe_benchmark.py:139), ``error`` (benchmark.py:28),
+``write_real_moe_trace`` / ``validate_real_moe_trace`` (moe_real_trace.py:267,448) -
 runs them on seeded CPU inputs, and stores inputs (small cases) or input
 digests (large cases) together with the reference's outputs.
 """
@@ -129,6 +130,51 @@ def main(ref_root):
                   "format_error": packed.metadata["weight_format_error"]}
     torch.save({"words": packed.words[5, 16:20].clone(), "scales": packed.scales[5, 16:20].clone(),
                 "source": w[5, 16:20].clone(), "dequant": deq[5, 16:20].clone()}, HERE / "w4_slice.pt")
+    # 6. real-trace bundle: a 6-token trace written by the REFERENCE's writer (committed: manifest + trace
+    #    tensors; the 1.8 GB weight bundle it references is the seeded layer, regenerated by the tests), and the
+    #    reverse direction: a bundle written by this package's writer passes the reference's validator.
+    import shutil
+    import tempfile
+    from llm_gpu_kernels import moe_real_trace as ref_trace
+    from llm_gpu_kernels_b200 import moe_real_trace as our_trace
+    g = torch.Generator().manual_seed(0)
+    wr = (0.02 * torch.randn(128, 2048, generator=g)).bfloat16()
+    gu = torch.empty(128, 1536, 2048, dtype=torch.bfloat16)
+    dn = torch.empty(128, 2048, 768, dtype=torch.bfloat16)
+    for e in range(128):
+        gu[e] = (0.02 * torch.randn(1536, 2048, generator=g)).bfloat16()
+    for e in range(128):
+        dn[e] = (0.02 * torch.randn(2048, 768, generator=g)).bfloat16()
+    x = torch.randn(6, 2048, generator=torch.Generator().manual_seed(31)).bfloat16()
+    ids, rw = router_formula(x, wr, 8)
+    rw = rw.bfloat16().float()      # the captured model's convention (capture script :587-588)
+    out_dir = HERE / "ref_trace"
+    shutil.rmtree(out_dir, ignore_errors=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        tmp = Path(tmp)
+        torch.save({"gate_up": gu, "down": dn}, tmp / "weights.pt")
+        weight_sha = ref_trace.sha256_file(tmp / "weights.pt")
+        ref = {name: {"path": "weights.pt", "tensor_name": name, "shape": list(t.shape), "dtype": "bfloat16",
+                      "sha256": weight_sha, "source_manifest_sha256": "0" * 64}
+               for name, t in (("gate_up", gu), ("down", dn))}
+        ref_trace.write_real_moe_trace(tmp / "trace.json", "trace.pt", x=x, expert_ids=ids, route_weights=rw,
+                                       provenance={"generator": "tests/golden/make_golden.py", "tokens": 6,
+                                                   "weights": "seeded_layer(seed 0), N(0, 0.02)"}, weights=ref)
+        ref_trace.validate_real_moe_trace(tmp / "trace.json")                 # the reference accepts its own bundle
+        ours = our_trace.validate_real_moe_trace(tmp / "trace.json", load_weights=True)   # and so does this package
+        assert torch.equal(ours.tensors["x"], x) and torch.equal(ours.weights["down"], dn)
+        out_dir.mkdir()
+        shutil.copy(tmp / "trace.json", out_dir / "trace.json")
+        shutil.copy(tmp / "trace.pt", out_dir / "trace.pt")
+        # the other direction
+        manifest = our_trace.write_real_moe_trace(tmp / "ours", x, ids, rw, gu, dn, provenance={"writer": "b200"})
+        accepted = ref_trace.validate_real_moe_trace(manifest, load_weights=True)
+        assert torch.equal(accepted.tensors["expert_ids"], ids)
+        meta["real_trace"] = {"weights_file_sha256": weight_sha, "gate_up_tensor_sha256": our_trace.tensor_sha256(gu),
+                              "down_tensor_sha256": our_trace.tensor_sha256(dn),
+                              "oracle_out_sha256": digest(moe_reference(x, gu, dn, ids, rw)),
+                              "our_writer_accepted_by_reference_validator": True}
+        torch.save({"out": moe_reference(x, gu, dn, ids, rw)}, out_dir / "reference_output.pt")
     (HERE / "golden_meta.json").write_text(json.dumps(meta, indent=1))
     print("golden fixtures written to", HERE)
 

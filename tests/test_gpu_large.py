@@ -174,3 +174,28 @@ def test_mixtral_shape_prefill_tile(dev, tile):
     m = check_rows(out, rows, x, gate_up, down, ids_cpu, rw_cpu, 5e-3, 8e-3)
     print(f"mixtral T={t} tile={tile} rows checked {rows.numel()} rel_rms={m['relative_rms']:.2e}")
     assert torch.equal(p.run(), out)
+
+
+def test_reference_written_trace_replays(dev, golden_dir, tmp_path):
+    """The committed bundle written by the reference's write_real_moe_trace, its weight bundle regenerated from
+    the seed (content hashes pinned in golden_meta.json), through prepare_trace_moe: the output must match the
+    reference's own moe_reference output stored beside the bundle."""
+    import json
+    import shutil
+    from llm_gpu_kernels_b200.moe_real_trace import prepare_trace_moe, tensor_sha256, validate_real_moe_trace
+    from tests.util import seeded_layer_per_expert
+    meta = json.loads((golden_dir / "golden_meta.json").read_text())["real_trace"]
+    _, gate_up, down = seeded_layer_per_expert(0, 2048, 768, 128)
+    assert tensor_sha256(gate_up) == meta["gate_up_tensor_sha256"] and tensor_sha256(down) == meta["down_tensor_sha256"]
+    for name in ("trace.json", "trace.pt"):
+        shutil.copy(golden_dir / "ref_trace" / name, tmp_path / name)
+    torch.save({"gate_up": gate_up, "down": down}, tmp_path / "weights.pt")
+    trace = validate_real_moe_trace(tmp_path / "trace.json", verify_hashes=False, load_weights=True)
+    prepared = prepare_trace_moe(trace, dev)
+    out = prepared.run()
+    torch.cuda.synchronize()
+    prepared.check_inputs()
+    want = torch.load(golden_dir / "ref_trace" / "reference_output.pt")["out"]
+    m = O.error_metrics(out.float().cpu(), want)
+    assert m["finite"] and m["relative_rms"] <= 5e-3 and m["normalized_max"] <= 8e-3, m
+    check_dispatch(prepared.base, trace.tensors["x"], trace.tensors["expert_ids"], 128)

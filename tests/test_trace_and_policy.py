@@ -32,6 +32,40 @@ def test_trace_round_trip(tmp_path):
     assert validate_real_moe_trace(manifest, load_trace=False).tensors is None
 
 
+def test_bundle_written_by_the_reference_is_accepted(golden_dir, tmp_path):
+    """tests/golden/ref_trace holds a manifest and a trace bundle written by the reference's own
+    write_real_moe_trace (see make_golden.py); the 1.8 GB weight bundle it points to is not committed."""
+    import shutil
+    for name in ("trace.json", "trace.pt"):
+        shutil.copy(golden_dir / "ref_trace" / name, tmp_path / name)
+    manifest = tmp_path / "trace.json"
+    trace = validate_real_moe_trace(manifest, check_weight_files=False)
+    assert tuple(trace.tensors["x"].shape) == (6, 2048) and tuple(trace.tensors["expert_ids"].shape) == (6, 8)
+    assert trace.manifest["model"]["num_experts"] == 128 and trace.manifest["status"] == "passed"
+    assert trace.manifest["trace"]["tensors"]["route_weights"]["sha256"] == tensor_sha256(trace.tensors["route_weights"])
+    with pytest.raises(ValueError, match="existing file"):
+        validate_real_moe_trace(manifest)                       # the weight bundle is required by default
+    with pytest.raises(ValueError, match="expected"):
+        validate_real_moe_trace(manifest, check_weight_files=False, dims=DIMS)
+    # every manifest rule of the reference's validator is enforced here too
+    good = json.loads(manifest.read_text())
+    for mutate, message in (
+            (lambda m: m.update(status="failed"), "not marked passed"),
+            (lambda m: m["routing_contract"].update(renormalization="topk"), "routing contract"),
+            (lambda m: m.pop("capture"), "capture metadata"),
+            (lambda m: m["trace"].update(format="pickle"), "weights-only tensor dictionary"),
+            (lambda m: m["weights"]["down"].update(format="pickle"), "weights-only torch bundle"),
+            (lambda m: m["weights"]["down"].update(source_manifest_sha256="1" * 64), "same layer-extraction"),
+            (lambda m: m["weights"]["gate_up"].update(shape=[128, 1536, 1024]), "shape/dtype"),
+            (lambda m: m["trace"]["tensors"]["x"].update(dtype="float32"), "dtype must be"),
+            (lambda m: m["model"].update(top_k=0), "model block")):
+        bad = json.loads(json.dumps(good))
+        mutate(bad)
+        manifest.write_text(json.dumps(bad))
+        with pytest.raises(ValueError, match=message):
+            validate_real_moe_trace(manifest, check_weight_files=False)
+
+
 def test_trace_tampering_is_detected(tmp_path):
     x, ids, rw, gu, dn = small_trace()
     manifest = write_real_moe_trace(tmp_path, x, ids, rw, gu, dn, dims=DIMS)

@@ -75,3 +75,17 @@ def zipf_routes(x, router_weight, topk, s, seed=0):
     logits = x.float() @ router_weight.float().T + zipf_bias(router_weight.shape[0], s, seed)
     weights, ids = torch.topk(torch.softmax(logits, dim=1), topk, dim=-1)
     return ids.to(torch.int32), (weights / weights.sum(-1, keepdim=True)).float()
+
+
+def seeded_layer_per_expert(seed, hidden, inter, experts, wscale=0.02):
+    """Router weight, gate_up, down with one FP32 draw per expert (the draw order of bench.py and of the
+    golden real-trace bundle); bounds the FP32 temporaries at the Qwen shape."""
+    g = torch.Generator().manual_seed(seed)
+    wr = (wscale * torch.randn(experts, hidden, generator=g)).bfloat16()
+    gate_up = torch.empty(experts, 2 * inter, hidden, dtype=torch.bfloat16)
+    down = torch.empty(experts, hidden, inter, dtype=torch.bfloat16)
+    for e in range(experts):
+        gate_up[e] = (wscale * torch.randn(2 * inter, hidden, generator=g)).bfloat16()
+    for e in range(experts):
+        down[e] = (wscale * torch.randn(hidden, inter, generator=g)).bfloat16()
+    return wr, gate_up, down
