@@ -268,7 +268,9 @@ def bench_tokens(tokens, weights, dev, steps, warmup, peaks, packed=None, shape=
 
     def build(x_, ids_, rw_):
         if packed is not None:
-            return prepare_w4_moe(x_, packed[0], None, ids_, rw_, packed_down=packed[1], router_weight=router)
+            from llm_gpu_kernels_b200.gemm import GemmConfig
+            return prepare_w4_moe(x_, packed[0], None, ids_, rw_, packed_down=packed[1], router_weight=router,
+                                  down_config=GemmConfig(block_m=token_tile) if token_tile else None)
         return prepare_ranked_moe_launcher(x_, gate_up, down, ids_, rw_, router_weight=router, token_tile=token_tile)
 
     if zipf > 0:

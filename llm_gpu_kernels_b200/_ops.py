@@ -14,6 +14,7 @@ the tensors passed per call for the tracer's benefit and the addresses fixed in 
 """
 from __future__ import annotations
 
+import weakref
 from typing import List
 
 import torch
@@ -21,6 +22,19 @@ import torch
 from . import _native
 
 _LIB_NAME = "b200moe::forward"
+_PLANS = {}   # plan address -> weak reference to the PreparedMoE that owns it
+
+
+def register_plan(prepared):
+    """Called by ``PreparedMoE.run()`` once: lets the operator find the tensors bound into the plan."""
+    key = prepared._plan.value
+    _PLANS[key] = weakref.ref(prepared, lambda _ref, key=key: _PLANS.pop(key, None))
+
+
+def _bound_tensors(prepared):
+    return [prepared.ids, prepared.routing_weights, prepared.output, prepared.counts, prepared.offsets,
+            prepared.cursors, prepared.tasks, prepared.mapping, prepared.ranks, prepared.grouped_input,
+            prepared.activated, prepared.down_output, prepared.status, prepared.scratch]
 
 
 @torch.library.custom_op(_LIB_NAME, mutates_args=("ids", "routing_weights", "output", "workspace"),
@@ -28,15 +42,29 @@ _LIB_NAME = "b200moe::forward"
 def forward(plan: int, x: torch.Tensor, weights: List[torch.Tensor], ids: torch.Tensor,
             routing_weights: torch.Tensor, output: torch.Tensor, workspace: List[torch.Tensor]) -> None:
     """One forward of the prepared plan ``plan`` (the ``B200MoePlan*`` as an integer) on the current stream of
-    ``x``'s device. The tensor arguments are the ones bound into the plan; they are passed so that PyTorch knows
-    what is read and what is written - the kernels use the addresses bound at prepare time."""
+    ``x``'s device. The kernels use the addresses bound at prepare time; the tensor arguments tell PyTorch what
+    is read and what is written. Normally they ARE the bound tensors and nothing else happens. A tracer that
+    functionalises the call (``torch.compile`` without re-inplacing) hands in copies instead: values of passed
+    inputs are then copied into the bound buffers before the forward and the bound results into the passed
+    tensors after it, so the op is a function of its arguments either way."""
     device = x.device
     lib = _native.load()
+    owner = _PLANS.get(plan)
+    prepared = owner() if owner is not None else None
+    passed = [ids, routing_weights, output, *workspace]
+    bound = _bound_tensors(prepared) if prepared is not None else passed
+    if prepared is not None:
+        for given, real in ((x, prepared.x), (ids, prepared.ids), (routing_weights, prepared.routing_weights)):
+            if given.data_ptr() != real.data_ptr():
+                real.copy_(given)
     if torch.cuda.current_device() == device.index:
         _native.check(lib.b200moe_forward(plan, torch.cuda.current_stream(device).cuda_stream))
     else:
         with torch.cuda.device(device):
             _native.check(lib.b200moe_forward(plan, torch.cuda.current_stream(device).cuda_stream))
+    for given, real in zip(passed, bound):
+        if given.data_ptr() != real.data_ptr():
+            given.copy_(real)
 
 
 @forward.register_fake

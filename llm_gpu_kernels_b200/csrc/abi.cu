@@ -359,6 +359,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     if ((rc = configure_tc(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && (rc = configure_w4(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && p->token_tile <= 64 && (rc = configure_w4t(*p))) return rc;
+    if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && w4r_serves(*p) && (rc = configure_w4r(*p))) return rc;
   }
   p->bound = true;
   return B200MOE_OK;
@@ -408,10 +409,13 @@ static int gate_up_stage(B200MoePlan* p, void* stream, bool chained) {
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_gate_up_generic(*p, s), "gate_up launch");
-  // W4: dequantised operand in tensor memory while two accumulator sets still fit beside it (tile <= 64),
-  // in shared memory above that
-  if (is_w4(p->shape.gate_up_format))
+  // W4: up to 16 rows per tile the weights are dequantised in registers (weight-streaming kernel); above, the
+  // dequantised operand goes to tensor memory while two accumulator sets still fit beside it (tile <= 64), to
+  // shared memory above that
+  if (is_w4(p->shape.gate_up_format)) {
+    if (w4r_serves(*p)) return check_cuda(launch_gate_up_w4r(*p, s, chained), "gate_up launch");
     return check_cuda(w4_in_tmem(p) ? launch_gate_up_w4t(*p, s, chained) : launch_gate_up_w4(*p, s, chained), "gate_up launch");
+  }
   return check_cuda(launch_gate_up_tc(*p, s, chained), "gate_up launch");
 }
 
@@ -425,8 +429,10 @@ static int down_stage(B200MoePlan* p, void* stream, bool chained) {
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->schedule != B200MOE_SCHEDULE_TCGEN05) return check_cuda(launch_down_generic(*p, s), "down launch");
-  if (is_w4(p->shape.down_format))
+  if (is_w4(p->shape.down_format)) {
+    if (w4r_serves(*p)) return check_cuda(launch_down_w4r(*p, s, chained), "down launch");
     return check_cuda(w4_in_tmem(p) ? launch_down_w4t(*p, s, chained) : launch_down_w4(*p, s, chained), "down launch");
+  }
   return check_cuda(launch_down_tc(*p, s, chained), "down launch");
 }
 

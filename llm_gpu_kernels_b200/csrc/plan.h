@@ -38,6 +38,9 @@ struct B200MoePlan {
   // the same for the variant that keeps the dequantised operand in tensor memory (token tile <= 128)
   int w4t_packed_gate_up = 0, w4t_operand_gate_up = 0, w4t_smem_gate_up = 0;
   int w4t_packed_down = 0, w4t_operand_down = 0, w4t_smem_down = 0;
+  // the weight-streaming W4A16 kernel (token tile <= 16): dequantisation in registers, mma.sync
+  int w4r_stages_gate_up = 0, w4r_smem_gate_up = 0;
+  int w4r_stages_down = 0, w4r_smem_down = 0;
 };
 
 namespace b200moe {
@@ -58,6 +61,9 @@ cudaError_t launch_gate_up_w4(const B200MoePlan& p, cudaStream_t s, bool chained
 cudaError_t launch_down_w4(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_gate_up_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
 cudaError_t launch_down_w4t(const B200MoePlan& p, cudaStream_t s, bool chained);
+cudaError_t launch_gate_up_w4r(const B200MoePlan& p, cudaStream_t s, bool chained);
+cudaError_t launch_down_w4r(const B200MoePlan& p, cudaStream_t s, bool chained);
+bool w4r_serves(const B200MoePlan& p);
 cudaError_t launch_combine(const B200MoePlan& p, cudaStream_t s);
 
 size_t router_smem_bytes(int hidden, int experts);
@@ -68,6 +74,7 @@ int configure_tc(B200MoePlan& p);
 int configure_router_tc(B200MoePlan& p);
 int configure_w4(B200MoePlan& p);
 int configure_w4t(B200MoePlan& p);
+int configure_w4r(B200MoePlan& p);
 
 // The router raises its timeout flag in a scratch word (the dispatch folds it into the
 // status word, which it resets every forward): int32 index of that word inside `scratch`.

@@ -143,6 +143,7 @@ class PreparedMoE:
             workspace = [self.counts, self.offsets, self.cursors, self.tasks, self.mapping, self.ranks,
                          self.grouped_input, self.activated, self.down_output, self.status, self.scratch]
             self._op_args = (self._plan.value, self.x, weights, self.ids, self.routing_weights, self.output, workspace)
+            _ops.register_plan(self)
         _ops.forward(*self._op_args)
         return self.output
 

@@ -24,14 +24,20 @@ def check(out, x, gate_up_deq, down_deq, ids, rw):
     return m
 
 
-def test_down_dequant_is_bit_exact(dev):
+@pytest.mark.parametrize("tile", [0, 16, 64])
+def test_down_dequant_is_bit_exact(dev, tile):
     """One-hot activation rows make the down GEMM print the dequantised operand itself:
-    down_output[row, c] must equal bf16_rn(q * scale) of weight [expert, c, k] exactly."""
+    down_output[row, c] must equal bf16_rn(q * scale) of weight [expert, c, k] exactly. Tile 16 is the
+    weight-streaming kernel (dequantisation in registers), 64 the tensor-memory operand, the default (128) the
+    shared-memory operand."""
+    from llm_gpu_kernels_b200.gemm import GemmConfig
     from llm_gpu_kernels_b200.moe_w4_cuda import prepare_w4_moe
     e, h, i, t, k = 3, 256, 256, 64, 2
     x, gate_up, down, ids, rw = make_inputs(t, e, k, h, i, seed=1, wscale=0.05)
     pg, pd = quantize_gate_up(gate_up), quantize_down(down)
-    p = prepare_w4_moe(x.to(dev), pg.to(dev), None, ids.to(dev), rw.to(dev), packed_down=pd.to(dev))
+    p = prepare_w4_moe(x.to(dev), pg.to(dev), None, ids.to(dev), rw.to(dev), packed_down=pd.to(dev),
+                       down_config=GemmConfig(block_m=tile) if tile else None)
+    assert p.base.token_tile == (tile or 128)
     base = p.base
     rows = t * k
     hot = torch.arange(rows) * 7 % i
@@ -51,6 +57,10 @@ def test_down_dequant_is_bit_exact(dev):
 @pytest.mark.parametrize("t,e,k,h,i,both,tile", [
     (40, 8, 2, 256, 128, False, 0), (40, 8, 2, 256, 128, True, 0), (130, 4, 4, 128, 384, True, 64),
     (300, 2, 1, 384, 256, True, 256), (9, 16, 8, 512, 128, False, 16),
+    # the weight-streaming kernel (tile 16): many token tiles per expert, K of one half stage (128) and of one and
+    # a half stages (384), 256-channel down tiles with a ragged upper half (H = 128, 384), I not a multiple of 16
+    (40, 8, 2, 256, 128, True, 16), (130, 4, 4, 128, 384, True, 16), (33, 4, 2, 384, 256, True, 16),
+    (20, 3, 1, 128, 72, False, 16), (5, 32, 4, 2048, 768, True, 16), (64, 2, 2, 1024, 128, True, 16),
 ])
 def test_w4_small_shapes(dev, t, e, k, h, i, both, tile):
     from llm_gpu_kernels_b200.gemm import GemmConfig
