@@ -76,7 +76,10 @@ typedef struct {
                              reference captured does (scripts/capture_qwen3_moe_layer0.py:587-588) */
   int32_t unchained;      /* 1: b200moe_forward separates gate/up and down by an ordinary kernel boundary instead of
                              chaining them through the per-expert completion counters (for A/B timing) */
-  int32_t reserved[1];
+  int32_t fused_gather;   /* 1: do not materialise grouped_input when the kernels allow it (BF16 tensor-core gate/up, or
+                             the W4 weight-streaming kernel): the dispatch writes source_rows instead of copying rows
+                             and the gate/up kernel gathers the token rows itself. B200MoeWorkspace.gathers reports
+                             what the plan resolved; grouped_input may then be NULL and is left untouched. */
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned
@@ -96,10 +99,11 @@ typedef struct {
   size_t status;        /* [1] int32 */
   size_t scratch;       /* dispatch partial histograms, router flag, tile counter and per-expert completion
                            counters of the chained GEMM kernels */
+  size_t source_rows;   /* [R] int32: token whose row each grouped row is (inverse of mapping; 0 unless gathers) */
   int32_t token_tile;   /* resolved tile */
   int32_t schedule;     /* resolved schedule */
   int32_t launches;     /* kernels one forward enqueues */
-  int32_t reserved;
+  int32_t gathers;      /* 1: gate/up gathers token rows through source_rows; grouped_input is not written */
 } B200MoeWorkspace;
 
 /* Device pointers. x, weights, ids, routing_weights belong to the caller;
@@ -130,6 +134,14 @@ typedef struct {
   const void* residual;        /* optional [T,H] bf16: output = bf16(float(residual) + float(bf16(layer result))),
                                   i.e. the layer followed by the model's residual add in BF16, in the combine kernel.
                                   May alias `output` is NOT allowed; NULL = no residual. No reference counterpart. */
+  /* Expert-owning side of expert parallelism only (external_dispatch plans, BF16 tensor-core schedule), both NULL
+   * otherwise: the down projection stores each result row straight into its token owner's buffer instead of
+   * down_output. ep_row_dest[row] = (owner rank << 24) | row index in that owner's return buffer, written by the
+   * senders next to the row itself; ep_return_bases = device array of B200MOE_EP_MAX_RANKS addresses, entry g =
+   * rank g's return buffer ([its routes, H] bf16) as mapped in this process. */
+  const void* ep_row_dest;
+  const void* ep_return_bases;
+  void* source_rows;           /* [R] int32 workspace, required when the plan gathers (B200MoeWorkspace.gathers) */
 } B200MoeBuffers;
 
 /* ABI version of the loaded library. */
@@ -231,7 +243,9 @@ typedef struct {
   int32_t capacity;               /* rows each rank's receive buffer holds */
   int32_t token_tile;             /* tile of the expert plan (for its `tasks` prefix) */
   int32_t ids_are_int64;
-  int32_t reserved[3];
+  int32_t fused_return;           /* 1: the expert plan's down projection returns the rows itself (ep_row_dest bound):
+                                     b200moe_ep_return_rows then only runs the closing barrier */
+  int32_t reserved[2];
   /* token-owning side (local) */
   const void* x;                  /* [tokens,H] bf16 */
   const void* ids;                /* [tokens,K] */
@@ -257,6 +271,9 @@ typedef struct {
   int32_t reserved2;
   void* expert_status;            /* [1] int32 status word of the expert plan, restarted by the count exchange every
                                      forward (that plan has no dispatch of its own to do it); may be NULL */
+  const void* mapping;            /* [tokens*K] int32 of the route-only plan: where each route's result row belongs in
+                                     this rank's return buffer; sent along with the row when row_dest_peers is set */
+  void* row_dest_peers[B200MOE_EP_MAX_RANKS];    /* [capacity] int32 per rank (ep_row_dest of its expert plan), or NULL */
 } B200MoeEpArgs;
 
 /* The int32 words (inside the bound `scratch` buffer) through which the two GEMM kernels of one forward

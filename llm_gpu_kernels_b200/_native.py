@@ -32,7 +32,7 @@ class Shape(ctypes.Structure):
     _fields_ = [(name, ctypes.c_int32) for name in (
         "tokens", "experts", "topk", "hidden", "intermediate", "ids_are_int64", "gate_up_format",
         "down_format", "schedule", "token_tile", "use_router", "route_only", "external_dispatch", "router_bf16_weights",
-        "unchained")] + [("reserved", ctypes.c_int32 * 1)]
+        "unchained", "fused_gather")]
 
 
 WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "ranks",
@@ -40,9 +40,9 @@ WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping
 
 
 class Workspace(ctypes.Structure):
-    _fields_ = [(name, ctypes.c_size_t) for name in WORKSPACE_BUFFERS] + [
+    _fields_ = [(name, ctypes.c_size_t) for name in WORKSPACE_BUFFERS + ("source_rows",)] + [
         ("token_tile", ctypes.c_int32), ("schedule", ctypes.c_int32), ("launches", ctypes.c_int32),
-        ("reserved", ctypes.c_int32)]
+        ("gathers", ctypes.c_int32)]
 
 
 INPUT_BUFFERS = ("x", "router_weight", "gate_up", "gate_up_scales", "down", "down_scales", "ids",
@@ -50,7 +50,8 @@ INPUT_BUFFERS = ("x", "router_weight", "gate_up", "gate_up_scales", "down", "dow
 
 
 class Buffers(ctypes.Structure):
-    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS + ("valid_routes", "residual")]
+    _fields_ = [(name, ctypes.c_void_p) for name in INPUT_BUFFERS + WORKSPACE_BUFFERS + (
+        "valid_routes", "residual", "ep_row_dest", "ep_return_bases", "source_rows")]
 
 
 class DispatchArgs(ctypes.Structure):
@@ -69,13 +70,14 @@ EP_MAX_RANKS = 8
 class EpArgs(ctypes.Structure):
     """``B200MoeEpArgs``: expert parallelism over peer memory."""
     _fields_ = [(name, ctypes.c_int32) for name in (
-        "rank", "world", "experts", "topk", "hidden", "tokens", "capacity", "token_tile", "ids_are_int64")] + [
-        ("reserved", ctypes.c_int32 * 3)] + [(name, ctypes.c_void_p) for name in (
+        "rank", "world", "experts", "topk", "hidden", "tokens", "capacity", "token_tile", "ids_are_int64",
+        "fused_return")] + [("reserved", ctypes.c_int32 * 2)] + [(name, ctypes.c_void_p) for name in (
             "x", "ids", "ranks", "counts", "expert_counts", "expert_offsets", "expert_tasks", "expert_rows",
             "expert_output", "tables", "status")] + [(name, ctypes.c_void_p * EP_MAX_RANKS) for name in (
                 "recv_rows_peers", "return_rows_peers", "all_counts_peers", "flags_peers")] + [
         ("expert_chain", ctypes.c_void_p), ("expert_chain_words", ctypes.c_int32), ("reserved2", ctypes.c_int32),
-        ("expert_status", ctypes.c_void_p)]
+        ("expert_status", ctypes.c_void_p), ("mapping", ctypes.c_void_p),
+        ("row_dest_peers", ctypes.c_void_p * EP_MAX_RANKS)]
 
 
 EXPORTS = {

@@ -32,9 +32,12 @@ def register_plan(prepared):
 
 
 def _bound_tensors(prepared):
-    return [prepared.ids, prepared.routing_weights, prepared.output, prepared.counts, prepared.offsets,
-            prepared.cursors, prepared.tasks, prepared.mapping, prepared.ranks, prepared.grouped_input,
-            prepared.activated, prepared.down_output, prepared.status, prepared.scratch]
+    bound = [prepared.ids, prepared.routing_weights, prepared.output, prepared.counts, prepared.offsets,
+             prepared.cursors, prepared.tasks, prepared.mapping, prepared.ranks, prepared.grouped_input,
+             prepared.activated, prepared.down_output, prepared.status, prepared.scratch]
+    if prepared.source_rows is not None:
+        bound.append(prepared.source_rows)
+    return bound
 
 
 @torch.library.custom_op(_LIB_NAME, mutates_args=("ids", "routing_weights", "output", "workspace"),

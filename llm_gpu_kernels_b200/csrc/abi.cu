@@ -191,6 +191,9 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
     tile = kGenericTile;
   } else if (tile == 0) {
     tile = auto_token_tile(r, s.experts);
+    // both projections W4: the weight-streaming kernel (dequantisation in registers) serves 16 rows per tile and
+    // beats the tensor-memory variant at its tile 32; the few experts above 16 rows take a second tile
+    if (tile == 32 && is_w4(s.gate_up_format) && is_w4(s.down_format)) tile = 16;
   } else if (tile != 16 && tile != 32 && tile != 64 && tile != 128 && tile != 256) {
     set_error("token_tile must be one of 16, 32, 64, 128, 256");
     return B200MOE_ERR_INVALID;
@@ -216,6 +219,9 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   }
   const int blocks = (p->partitions + kDispatchWarps - 1) / kDispatchWarps;
   p->chain_words = 1 + s.experts;
+  // gathering gate/up: the BF16 tensor-core kernel, or the W4 weight-streaming kernel (token tile 16)
+  p->gather = s.fused_gather && schedule == B200MOE_SCHEDULE_TCGEN05 && !s.route_only && !s.external_dispatch &&
+              r > 0 && (!is_w4(s.gate_up_format) || tile <= 16);
 
   B200MoeWorkspace& w = p->ws;
   const size_t T = s.tokens, H = s.hidden, I = s.intermediate, E = s.experts, R = r;
@@ -231,10 +237,14 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.down_output = R * H * 2;
   w.status = 4;
   w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 2 + E) * 4);
+  w.source_rows = p->gather ? R * 4 : 0;
+  w.gathers = p->gather ? 1 : 0;
+  if (p->gather) w.grouped_input = 0;
   w.token_tile = tile;
   w.schedule = schedule;
   w.launches = s.tokens == 0 ? 0 : (s.use_router ? 1 : 0) + (p->dispatch_fused ? 2 : 3) + (s.route_only ? 0 : 3);
   if (s.route_only == 2) w.launches -= 1;            // no row copy
+  if (p->gather && p->dispatch_fused) w.launches -= 1;  // no row copy kernel
   if (s.external_dispatch) w.launches = s.tokens == 0 ? 0 : 2;  // gate_up + down only
   *out = p;
   return B200MOE_OK;
@@ -294,7 +304,8 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     if (!s.external_dispatch)
       for (const Named& n : own_dispatch)
         if (!check(n)) return B200MOE_ERR_INVALID;
-    if (s.route_only != 2 && !check({b->grouped_input, "grouped_input"})) return B200MOE_ERR_INVALID;
+    if (s.route_only != 2 && !p->gather && !check({b->grouped_input, "grouped_input"})) return B200MOE_ERR_INVALID;
+    if (p->gather && !check({b->source_rows, "source_rows"})) return B200MOE_ERR_INVALID;
     if (!s.external_dispatch && s.ids_are_int64 && reinterpret_cast<uintptr_t>(b->ids) % 8) {
       set_error("buffer 'ids' (int64) is not 8-byte aligned");
       return B200MOE_ERR_INVALID;
@@ -313,6 +324,18 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
           return B200MOE_ERR_INVALID;
         }
   }
+  if (b->ep_row_dest || b->ep_return_bases) {
+    if (!b->ep_row_dest || !b->ep_return_bases || !s.external_dispatch || p->schedule != B200MOE_SCHEDULE_TCGEN05 ||
+        is_w4(s.down_format)) {
+      set_error("ep_row_dest / ep_return_bases go together and need an external_dispatch plan on the BF16 "
+                "tensor-core schedule");
+      return B200MOE_ERR_INVALID;
+    }
+    if (reinterpret_cast<uintptr_t>(b->ep_row_dest) % 4 || reinterpret_cast<uintptr_t>(b->ep_return_bases) % 8) {
+      set_error("ep_row_dest / ep_return_bases are misaligned");
+      return B200MOE_ERR_INVALID;
+    }
+  }
   p->buf = *b;
   p->router_tc = false;
   if (s.tokens > 0 && s.use_router && p->schedule == B200MOE_SCHEDULE_TCGEN05 &&
@@ -329,7 +352,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     }
   }
   if (s.tokens > 0 && p->schedule == B200MOE_SCHEDULE_TCGEN05 && !s.route_only) {
-    const void* aligned16[] = {b->gate_up, b->down, b->grouped_input, b->activated};
+    const void* aligned16[] = {b->gate_up, b->down, p->gather ? b->x : b->grouped_input, b->activated};
     for (const void* ptr : aligned16)
       if (reinterpret_cast<uintptr_t>(ptr) % 16) {
         set_error("tcgen05 schedule: weights and workspace rows must be 16-byte aligned");
@@ -354,7 +377,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
     } else if ((rc = encode_2d(&p->tm_down_w, b->down, E * H, I, 128, true))) {
       return rc;
     }
-    if ((rc = encode_2d(&p->tm_grouped, b->grouped_input, R, H, p->token_tile, false))) return rc;
+    if (!p->gather && (rc = encode_2d(&p->tm_grouped, b->grouped_input, R, H, p->token_tile, false))) return rc;
     if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->token_tile, false))) return rc;
     if ((rc = configure_tc(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && (rc = configure_w4(*p))) return rc;

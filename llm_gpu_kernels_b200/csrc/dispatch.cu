@@ -22,6 +22,8 @@
 //            the token-tile prefix `tasks`, cursors = 0, and the status word.
 //  permute - ranks[q] += base; mapping[q] = offsets[id] + ranks[q]; one warp
 //            copies the token's row to grouped_input[mapping[q]].
+// A plan whose gate/up kernel gathers the token rows itself gets source_rows[mapping[q]] = q / K (the inverse
+// permutation) instead of the row copy.
 #include <cuda_bf16.h>
 #include "plan.h"
 #include "pdl.cuh"
@@ -159,7 +161,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
                       int* __restrict__ mapping, int* __restrict__ counts, int* __restrict__ offsets,
                       int* __restrict__ cursors, int* __restrict__ tasks, int* __restrict__ status,
                       int* __restrict__ router_flag, const int* __restrict__ valid_routes, int R, int E,
-                      int warp_routes, int token_tile, int chain_words) {
+                      int warp_routes, int token_tile, int chain_words, int* __restrict__ source_rows, int K) {
   pdl_launch_dependents();
   pdl_wait();  // ids / routing weights may come from the router kernel just before
   const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
@@ -239,6 +241,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
       }
       ranks[q] = rank;
       mapping[q] = pos;
+      if (source_rows != nullptr && pos >= 0) source_rows[pos] = q / K;
     }
   }
 }
@@ -271,7 +274,7 @@ dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restri
                         const int* __restrict__ hist, const int* __restrict__ offsets,
                         int* __restrict__ ranks, int* __restrict__ mapping,
                         __nv_bfloat16* __restrict__ grouped, const int* __restrict__ valid_routes, int R, int E,
-                        int H, int K, int warp_routes) {
+                        int H, int K, int warp_routes, int* __restrict__ source_rows) {
   pdl_launch_dependents();
   pdl_wait();  // offsets and partition base ranks come from the scan kernel
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -287,6 +290,7 @@ dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restri
       const int rank = ranks[q] + hist[static_cast<size_t>(part) * E + static_cast<int>(id)];
       pos = offsets[id] + rank;
       ranks[q] = rank;
+      if (source_rows != nullptr) source_rows[pos] = q / K;
     }
     mapping[q] = pos;
   }
@@ -301,6 +305,29 @@ dispatch_permute_kernel(const __nv_bfloat16* __restrict__ x, const IdT* __restri
   } else {
     for (int i = lane; i < H; i += 32) dst[i] = src[i];
   }
+}
+
+// The permute step without the row copy (the rows are gathered by the gate/up kernel or sent to other ranks):
+// one thread per route.
+template <typename IdT>
+__global__ void __launch_bounds__(kThreads)
+dispatch_map_kernel(const IdT* __restrict__ ids, const int* __restrict__ hist, const int* __restrict__ offsets,
+                    int* __restrict__ ranks, int* __restrict__ mapping, const int* __restrict__ valid_routes, int R,
+                    int E, int K, int warp_routes, int* __restrict__ source_rows) {
+  pdl_launch_dependents();
+  pdl_wait();  // offsets and partition base ranks come from the scan kernel
+  const int q = blockIdx.x * kThreads + threadIdx.x;
+  if (q >= R) return;
+  const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;
+  const long long id = q < r_eff ? static_cast<long long>(ids[q]) : -1;
+  int pos = -1;
+  if (id >= 0 && id < E) {
+    const int rank = ranks[q] + hist[static_cast<size_t>(q / warp_routes) * E + static_cast<int>(id)];
+    pos = offsets[id] + rank;
+    ranks[q] = rank;
+    if (source_rows != nullptr) source_rows[pos] = q / K;
+  }
+  mapping[q] = pos;
 }
 
 }  // namespace
@@ -322,16 +349,17 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     auto* tasks = static_cast<int*>(p.buf.tasks);
     auto* status = static_cast<int*>(p.buf.status);
     auto* mapping = static_cast<int*>(p.buf.mapping);
+    int* source_rows = p.gather ? static_cast<int*>(p.buf.source_rows) : nullptr;
     if (sh.ids_are_int64) {
       launch_pdl(dispatch_fused_kernel<long long>, dim3(1), dim3(1024), 0, s, static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
                                                           counts, offsets, cursors, tasks, status, router_flag, valid, R,
-                                                          E, p.warp_routes, p.token_tile, p.chain_words);
+                                                          E, p.warp_routes, p.token_tile, p.chain_words, source_rows, sh.topk);
     } else {
       launch_pdl(dispatch_fused_kernel<int>, dim3(1), dim3(1024), 0, s, static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
                                                     offsets, cursors, tasks, status, router_flag, valid, R, E,
-                                                    p.warp_routes, p.token_tile, p.chain_words);
+                                                    p.warp_routes, p.token_tile, p.chain_words, source_rows, sh.topk);
     }
-    if (sh.route_only != 2)  // 2: the rows are sent straight to their expert owners instead
+    if (sh.route_only != 2 && !p.gather)  // the rows are sent to their expert owners / gathered by gate/up instead
       launch_pdl(dispatch_copy_kernel, dim3((R + kWarps - 1) / kWarps), dim3(kThreads), 0, s,
           static_cast<const __nv_bfloat16*>(p.buf.x), static_cast<const int*>(mapping), static_cast<__nv_bfloat16*>(p.buf.grouped_input), R,
           sh.hidden, sh.topk);
@@ -348,17 +376,31 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
       hist, flags, static_cast<int*>(p.buf.counts), static_cast<int*>(p.buf.offsets),
       static_cast<int*>(p.buf.cursors), static_cast<int*>(p.buf.tasks), static_cast<int*>(p.buf.status),
       hist + router_flag_index(p), E, p.partitions, blocks, p.token_tile, p.chain_words);
-  const int pblocks = (R + kWarps - 1) / kWarps;
   auto* x = static_cast<const __nv_bfloat16*>(p.buf.x);
-  auto* grouped = sh.route_only == 2 ? nullptr : static_cast<__nv_bfloat16*>(p.buf.grouped_input);
+  auto* grouped = (sh.route_only == 2 || p.gather) ? nullptr : static_cast<__nv_bfloat16*>(p.buf.grouped_input);
+  int* source_rows = p.gather ? static_cast<int*>(p.buf.source_rows) : nullptr;
+  if (grouped == nullptr) {
+    const int mblocks = (R + kThreads - 1) / kThreads;
+    if (sh.ids_are_int64) {
+      launch_pdl(dispatch_map_kernel<long long>, dim3(mblocks), dim3(kThreads), 0, s,
+          static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
+          static_cast<int*>(p.buf.mapping), valid, R, E, sh.topk, p.warp_routes, source_rows);
+    } else {
+      launch_pdl(dispatch_map_kernel<int>, dim3(mblocks), dim3(kThreads), 0, s,
+          static_cast<const int*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
+          static_cast<int*>(p.buf.mapping), valid, R, E, sh.topk, p.warp_routes, source_rows);
+    }
+    return cudaPeekAtLastError();
+  }
+  const int pblocks = (R + kWarps - 1) / kWarps;
   if (sh.ids_are_int64) {
     launch_pdl(dispatch_permute_kernel<long long>, dim3(pblocks), dim3(kThreads), 0, s,
         x, static_cast<const long long*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
-        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
+        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes, source_rows);
   } else {
     launch_pdl(dispatch_permute_kernel<int>, dim3(pblocks), dim3(kThreads), 0, s,
         x, static_cast<const int*>(p.buf.ids), hist, static_cast<const int*>(p.buf.offsets), ranks,
-        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes);
+        static_cast<int*>(p.buf.mapping), grouped, valid, R, E, sh.hidden, sh.topk, p.warp_routes, source_rows);
   }
   return cudaPeekAtLastError();
 }

@@ -176,6 +176,9 @@ ep_send_kernel(const B200MoeEpArgs a) {
   }
   copy_row(static_cast<const __nv_bfloat16*>(a.x) + static_cast<size_t>(q / a.topk) * a.hidden,
            static_cast<__nv_bfloat16*>(a.recv_rows_peers[owner]) + static_cast<size_t>(row) * a.hidden, a.hidden, lane);
+  // the way back: the owner's down projection stores this row's result at mapping[q] of my return buffer
+  if (lane == 0 && a.row_dest_peers[owner] && a.mapping)
+    static_cast<int*>(a.row_dest_peers[owner])[row] = (a.rank << 24) | static_cast<const int*>(a.mapping)[q];
 }
 
 // One warp per received row: its result goes back to the source rank, at the route's grouped position.
@@ -209,7 +212,8 @@ int check_args(const B200MoeEpArgs* a) {
   }
   if (a->world < 1 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world || a->experts < 1 ||
       a->experts > kMaxExperts || a->experts % a->world || a->topk < 1 || a->topk > 32 || a->hidden <= 0 ||
-      a->tokens < 0 || a->capacity <= 0 || a->token_tile <= 0) {
+      a->tokens < 0 || a->capacity <= 0 || a->token_tile <= 0 ||
+      static_cast<long long>(a->tokens) * a->topk >= (1 << 24)) {
     set_error("expert parallel: needs 1 <= world <= 8, experts <= 256 divisible by world, K <= 32, H > 0");
     return B200MOE_ERR_INVALID;
   }
@@ -307,7 +311,7 @@ int b200moe_ep_return_rows(const B200MoeEpArgs* a, void* stream) {
   int rc = check_args(a);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  ep_return_kernel<<<(a->capacity + 7) / 8, 256, 0, s>>>(*a);
+  if (!a->fused_return) ep_return_kernel<<<(a->capacity + 7) / 8, 256, 0, s>>>(*a);
   ep_barrier_kernel<<<1, 32, 0, s>>>(*a, 2);
   return launched("ep return launch");
 }

@@ -52,6 +52,9 @@ using namespace tile;
 
 constexpr int kThreads = 224;
 constexpr int kMmaWarpB = 6;  // second MMA-issuing warp
+constexpr int kGatherWarps = 4;                              // warps 7..10 of the gathering gate/up kernel
+constexpr int kGatherThreads = kThreads + 32 * kGatherWarps;
+constexpr int kGatherMaxIters = 16;                           // 16-byte chunks per gather lane and stage: tile 256
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
@@ -75,13 +78,23 @@ static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 // boundaries). The gate/up kernel adds one per epilogue warp and tile; the down kernel, given
 // chain_need = arrivals per token tile of an expert, waits for them before it loads activated rows.
 // tile_counter (down kernel only): global tile counter of the dynamic schedule, zero at launch.
-template <bool kGateUp>
-__global__ void __launch_bounds__(kThreads, 1)
+// row_dest / ret_bases (down kernel of an expert-parallel expert plan, else null): the result rows are stored
+// straight into their token owners' buffers over NVLink (see store_tile).
+// kGather (gate/up only): the rows of a tile are not read from an expert-contiguous copy but gathered from the
+// token rows themselves: source_rows[r] = token whose row grouped row r is (written by the dispatch), x = [T, k_dim].
+// Four extra warps copy 16-byte chunks with cp.async into the 128-byte-swizzled activation tile of each stage
+// (what the TMA box load would have written) and arrive on the stage's barrier through
+// cp.async.mbarrier.arrive, so the copies of several stages are in flight and no register holds data.
+template <bool kGateUp, bool kGather = false>
+__global__ void __launch_bounds__(kGather ? kGatherThreads : kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_act,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ g_offsets,
                        const int* __restrict__ g_counts, const int* __restrict__ g_tasks, int* __restrict__ status,
                        int E, int n_out, int k_dim, int w_rows_per_expert, int token_tile, int num_stages,
-                       int stream_weights, int* chain_done, int chain_need, int* tile_counter) {
+                       int stream_weights, int* chain_done, int chain_need, int* tile_counter,
+                       const int* row_dest, const unsigned long long* ret_bases,
+                       const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows) {
+  static_assert(kGateUp || !kGather, "only the gate/up projection gathers token rows");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -101,7 +114,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (!kGateUp) pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
-      mbar_init(&c->full[s], 1);
+      mbar_init(&c->full[s], kGather ? 1 + 32 * kGatherWarps : 1);   // TMA (+ every gather lane's copies)
       mbar_init(&c->empty[s], 2);   // the commits of the two MMA issuers
     }
     for (int a = 0; a < 2; ++a) {
@@ -157,10 +170,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status)) { ok = false; break; }
           unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
-          mbar_expect_tx(&c->full[stage], stage_bytes);
+          mbar_expect_tx(&c->full[stage], kGather ? kWBytes : stage_bytes);
           tma_load_2d(st, &tm_w, &c->full[stage], kb * kBlockK, w_row, pol_w);
           if (kGateUp) tma_load_2d(st + kWTileBytes, &tm_w, &c->full[stage], kb * kBlockK, w_row + n_out, pol_w);
-          tma_load_2d(st + kWBytes, &tm_act, &c->full[stage], kb * kBlockK, t.row0, pol_act);
+          if (!kGather) tma_load_2d(st + kWBytes, &tm_act, &c->full[stage], kb * kBlockK, t.row0, pol_act);
           ++issued;
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
         }
@@ -193,6 +206,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&c->full[stage], phase, &c->abort, status)) { ok = false; break; }
           tc_fence_after();
+          if (kGather) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async-written rows -> MMA
           const uint32_t w_addr = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
           const uint32_t a_addr = w_addr + kWBytes;
 #pragma unroll
@@ -217,6 +231,47 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         mbar_wait_plain(&c->drain[half], 0);
       }
     }
+  } else if (kGather && warp > kMmaWarpB) {
+    // ------------------------------------------------------------------ gather warps: token rows -> activation tile
+    const int gt = (warp - kMmaWarpB - 1) * 32 + lane;   // 0..127
+    const int chunk = gt & 7;                            // 16-byte chunk of the 128-byte k-block row
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int seq = 0; ok; ++seq) {
+      const int item = follow_item(c, false, seq, total_items, status);
+      if (item < 0) break;
+      const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
+      const int iters = (t.rows * 8 + 32 * kGatherWarps - 1) / (32 * kGatherWarps);   // <= kGatherMaxIters
+      int src[kGatherMaxIters];   // element offset of row n = it*16 + gt/8 in x, -1 past the tile's rows
+#pragma unroll
+      for (int it = 0; it < kGatherMaxIters; ++it) {
+        const int n = it * 16 + (gt >> 3);
+        src[it] = (it < iters && n < t.rows) ? source_rows[t.row0 + n] * k_dim : -1;
+      }
+      for (int kb = 0; kb < num_kb; ++kb) {
+        int free_ok = 1;
+        if (lane == 0) free_ok = mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status) ? 1 : 0;
+        free_ok = __shfl_sync(0xffffffffu, free_ok, 0);
+        if (!free_ok) { ok = false; break; }
+        const uint32_t act = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes) + kWBytes;
+        const int k = kb * kBlockK + chunk * 8;
+        const uint32_t bytes = k < k_dim ? 16u : 0u;       // a chunk past K is zero-filled, as the TMA load did
+#pragma unroll
+        for (int it = 0; it < kGatherMaxIters; ++it) {
+          if (it < iters && src[it] >= 0) {
+            const int n = it * 16 + (gt >> 3);
+            const uint32_t dst = act + static_cast<uint32_t>(n) * 128u + (static_cast<uint32_t>(chunk ^ (n & 7)) << 4);
+            const __nv_bfloat16* from = x + src[it] + (bytes ? k : 0);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(from), "r"(bytes) : "memory");
+          }
+        }
+        // one arrival per lane once its copies above have landed (the barrier expects every gather lane)
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&c->full[stage])) : "memory");
+        if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");   // never leave with copies in flight
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -230,7 +285,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out,
+                                    kGateUp ? nullptr : row_dest, ret_bases);
       tc_fence_before();
       if (kGateUp && chain_done != nullptr) {
         // this lane's rows were written through the generic proxy and the down kernel reads them through the
@@ -264,7 +320,7 @@ int stages_for(bool gate_up, int token_tile, int* smem_bytes) {
   return stages;
 }
 
-template <bool kGateUp>
+template <bool kGateUp, bool kGather = false>
 cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
@@ -276,7 +332,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const int stages = kGateUp ? p.gemm_stages_gate_up : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
-  launch_pdl(grouped_gemm_tc_kernel<kGateUp>, dim3(grid), dim3(kThreads), smem, s,
+  launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
@@ -284,7 +340,10 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
       kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, stages, stream_weights,
       chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
       4 * ((sh.intermediate + kTileM - 1) / kTileM),  // epilogue warps x gate/up channel tiles per token tile
-      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr));
+      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr),
+      kGateUp ? static_cast<const int*>(nullptr) : static_cast<const int*>(p.buf.ep_row_dest),
+      static_cast<const unsigned long long*>(p.buf.ep_return_bases), static_cast<const __nv_bfloat16*>(p.buf.x),
+      static_cast<const int*>(p.buf.source_rows));
   return cudaPeekAtLastError();
 }
 
@@ -303,6 +362,9 @@ int configure_tc(B200MoePlan& p) {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemLimit);
   if (e != cudaSuccess) {
     set_error("cudaFuncSetAttribute(shared memory) failed: %s", cudaGetErrorString(e));
     return B200MOE_ERR_CUDA;
@@ -311,7 +373,7 @@ int configure_tc(B200MoePlan& p) {
 }
 
 cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
-  return launch_tc<true>(p, s, chained);
+  return p.gather ? launch_tc<true, true>(p, s, chained) : launch_tc<true>(p, s, chained);
 }
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   return launch_tc<false>(p, s, chained);

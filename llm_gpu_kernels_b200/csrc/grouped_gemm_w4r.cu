@@ -91,25 +91,79 @@ __device__ __forceinline__ uint4 ldg_cg128(const void* p) {
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// (a & b) | c in ONE logic instruction. Left to itself the compiler keeps both constants as immediates and spends
+// two instructions per nibble pair; with the constants in registers the three-input form takes one.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // One packed word -> four BF16 pairs {k_j, k_(j+4)}, j = 0..3, each bf16_rn(q * scale).
-__device__ __forceinline__ void dequant_pairs(uint32_t w, __nv_bfloat162 scale2, uint32_t (&pair)[4]) {
+// mask = 0x000F000F and magic = 0x43004300 come in as registers the compiler cannot see through.
+__device__ __forceinline__ void dequant_pairs(uint32_t w, __nv_bfloat162 scale2, uint32_t mask, uint32_t magic,
+                                              uint32_t (&pair)[4]) {
   const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;   // {128 + n_j, 128 + n_(j+4)}
+    uint32_t v = and_or(w >> (4 * j), mask, magic);   // {128 + n_j, 128 + n_(j+4)}
     __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);   // exact
     q = __hmul2(q, scale2);                                                       // the one rounding
     pair[j] = *reinterpret_cast<uint32_t*>(&q);
   }
 }
 
+// One consumer warp's share of one stage: 128 K (four 32-K chunks) of its 16 channel rows in both weight boxes,
+// against kNT column tiles of 8 rows. w_base: the stage; b_base: the activation tile at this thread's row g.
+template <int kNT>
+__device__ __forceinline__ void multiply_half(float (&acc)[2][kMaxNT][4], uint32_t w_base, uint32_t b_base,
+                                              const __nv_bfloat162 (&sc)[2][2], int group, uint32_t lm_row,
+                                              uint32_t lm_chunk, int t4, int g, uint32_t mask, uint32_t magic) {
+  // all packed words of this stage half first: the loads overlap the arithmetic of the chunks before
+  uint32_t wl[2][4], wh[2][4];
+#pragma unroll
+  for (int c2l = 0; c2l < 2; ++c2l) {
+    const uint32_t c2 = static_cast<uint32_t>(group * 2 + c2l);
+    const uint32_t lm = lm_row * 128u + (((c2 * 2u + lm_chunk) ^ (lm_row & 7u)) << 4);
+    ldmatrix_x4(wl[c2l], w_base + lm);
+    ldmatrix_x4(wh[c2l], w_base + kBoxBytes + lm);
+  }
+  const uint32_t flip = static_cast<uint32_t>(g & 1) << 2;
+#pragma unroll
+  for (int c2l = 0; c2l < 2; ++c2l) {
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const uint32_t gidx = static_cast<uint32_t>(((group * 2 + c2l) * 2 + cc) * 4 + t4);
+      const uint32_t b_off = (gidx ^ flip) << 4;
+      uint4 b[kNT];
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) b[nt] = lds128(b_base + nt * 8 * kRowBytes + b_off);
+      uint32_t a[2][2][4];   // [box][row g / g+8][pair]
+      dequant_pairs(wl[c2l][2 * cc], sc[0][0], mask, magic, a[0][0]);
+      dequant_pairs(wl[c2l][2 * cc + 1], sc[0][1], mask, magic, a[0][1]);
+      dequant_pairs(wh[c2l][2 * cc], sc[1][0], mask, magic, a[1][0]);
+      dequant_pairs(wh[c2l][2 * cc + 1], sc[1][1], mask, magic, a[1][1]);
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma_bf16(acc[h][nt], a[h][0][0], a[h][1][0], a[h][0][1], a[h][1][1], b[nt].x, b[nt].y);
+          mma_bf16(acc[h][nt], a[h][0][2], a[h][1][2], a[h][0][3], a[h][1][3], b[nt].z, b[nt].w);
+        }
+      }
+    }
+  }
+}
+
 // act: the rows the tile multiplies ([R, k_dim] BF16, dense ragged expert segments). hi_offset: row distance of the
 // second weight box (the up rows: n_out; the upper half of a 256-channel down tile: 128). tile_channels: output
 // channels of one tile (128 gate/up, 256 down). chain_done / chain_need / tile_counter: as in the BF16 kernel.
+// source_rows (gate/up of a gathering plan, else null): `act` is the token matrix x and grouped row r is its row
+// source_rows[r] - the dispatch then copies no rows at all.
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv_bfloat16* act,
@@ -117,7 +171,8 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
                         const int* __restrict__ g_offsets, const int* __restrict__ g_counts,
                         const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
                         int w_rows_per_expert, int token_tile, int num_stages, int stream_weights, int hi_offset,
-                        int tile_channels, int* chain_done, int chain_need, int* tile_counter) {
+                        int tile_channels, int* chain_done, int chain_need, int* tile_counter,
+                        const int* __restrict__ source_rows) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -210,6 +265,12 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
       }
       const int n_pad = (t.rows + 7) & ~7;                 // rows of the n8 column tiles in use
       const int items = n_pad * (kStageK / 8);             // 16-byte groups of one stage
+      int src_row[kMaxTile / 2];                           // the row of `act` behind each of this lane's groups
+#pragma unroll
+      for (int j = 0; j < kMaxTile / 2; ++j) {
+        const int n = (j * kRowWarps + rw), r = t.row0 + min(n, t.rows - 1);
+        src_row[j] = (n < n_pad && source_rows != nullptr) ? source_rows[r] : r;
+      }
       for (int s = 0; s < num_ks; ++s) {
         int free_ok = 1;
         if (lane == 0) free_ok = mbar_wait(&c->empty[stage], phase ^ 1u, &c->abort, status) ? 1 : 0;
@@ -220,9 +281,9 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
 #pragma unroll
         for (int j = 0; j < kMaxTile / 2; ++j) {           // loads first: one L2 latency for the whole stage
           const int i = (j * kRowWarps + rw) * 32 + lane;
-          const int n = i >> 5, k = s * kStageK + (i & 31) * 8;
+          const int k = s * kStageK + (i & 31) * 8;
           if (i < items && k < k_dim)
-            v[j] = ldg_cg128(act + static_cast<size_t>(t.row0 + min(n, t.rows - 1)) * k_dim + k);
+            v[j] = ldg_cg128(act + static_cast<size_t>(src_row[j]) * k_dim + k);
         }
 #pragma unroll
         for (int j = 0; j < kMaxTile / 2; ++j) {
@@ -253,6 +314,8 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
     // for two consecutive 16-byte chunks (32 K each) of the 128-byte row
     const uint32_t lm_row = static_cast<uint32_t>(blk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7));
     const uint32_t lm_chunk = static_cast<uint32_t>(lane >> 4);
+    uint32_t mask = 0x000F000Fu, magic = 0x43004300u;   // made opaque once: see and_or()
+    asm volatile("" : "+r"(mask), "+r"(magic));
     bool ok = true;
     for (int seq = 0; ok; ++seq) {
       const int item = follow_item(c, dynamic, seq, total_items, status);
@@ -300,36 +363,9 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
           if (!__all_sync(0xffffffffu, mbar_wait(&c->full[stage], phase, &c->abort, status))) { ok = false; break; }
           const uint32_t w_base = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
           const uint32_t b_base = w_base + 2 * kBoxBytes + static_cast<uint32_t>(g) * kRowBytes;
-#pragma unroll
-          for (int c2l = 0; c2l < 2; ++c2l) {
-            const int c2 = group * 2 + c2l;
-            if (c2l * 64 < k_left) {
-              uint32_t wl[4], wh[4];
-              const uint32_t lm = lm_row * 128u + (((static_cast<uint32_t>(c2) * 2u + lm_chunk) ^ (lm_row & 7u)) << 4);
-              ldmatrix_x4(wl, w_base + lm);
-              ldmatrix_x4(wh, w_base + kBoxBytes + lm);
-#pragma unroll
-              for (int cc = 0; cc < 2; ++cc) {
-                uint32_t a[2][2][4];   // [box][row g / g+8][pair]
-                dequant_pairs(wl[2 * cc], sc[0][0], a[0][0]);
-                dequant_pairs(wl[2 * cc + 1], sc[0][1], a[0][1]);
-                dequant_pairs(wh[2 * cc], sc[1][0], a[1][0]);
-                dequant_pairs(wh[2 * cc + 1], sc[1][1], a[1][1]);
-                const uint32_t gidx = static_cast<uint32_t>((c2 * 2 + cc) * 4 + t4);
-                const uint32_t b_off = (gidx ^ (static_cast<uint32_t>(g & 1) << 2)) << 4;
-#pragma unroll
-                for (int nt = 0; nt < kMaxNT; ++nt) {
-                  if (nt < n_tiles) {
-                    const uint4 b = lds128(b_base + nt * 8 * kRowBytes + b_off);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                      mma_bf16(acc[h][nt], a[h][0][0], a[h][1][0], a[h][0][1], a[h][1][1], b.x, b.y);
-                      mma_bf16(acc[h][nt], a[h][0][2], a[h][1][2], a[h][0][3], a[h][1][3], b.z, b.w);
-                    }
-                  }
-                }
-              }
-            }
+          if (k_left > 0) {   // K is a multiple of 128: a stage half is whole or absent
+            if (n_tiles == 1) multiply_half<1>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, mask, magic);
+            else multiply_half<2>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, mask, magic);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&c->empty[stage]);
@@ -415,7 +451,7 @@ cudaError_t launch_w4r(const B200MoePlan& p, cudaStream_t s, bool chained) {
   launch_pdl(grouped_gemm_w4r_kernel<kGateUp>, dim3(grid), dim3(kThreads),
              static_cast<size_t>(kGateUp ? p.w4r_smem_gate_up : p.w4r_smem_down), s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w,
-      static_cast<const __nv_bfloat16*>(kGateUp ? p.buf.grouped_input : p.buf.activated),
+      static_cast<const __nv_bfloat16*>(kGateUp ? (p.gather ? p.buf.x : p.buf.grouped_input) : p.buf.activated),
       static_cast<const __nv_bfloat16*>(kGateUp ? p.buf.gate_up_scales : p.buf.down_scales),
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
@@ -424,7 +460,8 @@ cudaError_t launch_w4r(const B200MoePlan& p, cudaStream_t s, bool chained) {
       stream_weights, kGateUp ? sh.intermediate : 128, tile_channels,
       chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
       kGroupWarps * ((sh.intermediate + 127) / 128),  // storing warps x gate/up channel tiles per token tile
-      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr));
+      chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr),
+      kGateUp && p.gather ? static_cast<const int*>(p.buf.source_rows) : static_cast<const int*>(nullptr));
   return cudaPeekAtLastError();
 }
 

@@ -19,6 +19,7 @@ struct B200MoePlan {
   int warp_routes = 0;
   int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
   bool dispatch_fused = false;  // one-block count + scan + mapping (R <= kFusedRoutes)
+  bool gather = false;          // gate/up reads token rows through source_rows; the dispatch copies no rows
   int chain_words = 0;     // scratch words after the router flag that the dispatch zeroes: tile counter + done[E]
   // TMA descriptors (tcgen05 schedule)
   CUtensorMap tm_gate_up_w{};   // [E*2I, H] bf16, box 64 x 128  (W4: [E*2I, H/8] int32, box 8 x 128)

@@ -90,6 +90,10 @@ class PreparedMoE:
     launches: tuple = ()
     kernel_launches: int = 0  # kernels one run() enqueues
     chain: tuple = None       # expert-side plans: (device address, count) of the int32 words the exchange zeroes
+    gathers: bool = False     # gate/up gathers token rows through source_rows; grouped_input is empty
+    source_rows: torch.Tensor = None   # [R] int32: the token behind each grouped row (only when gathers)
+    fused_return: bool = False  # expert-side plans: the down projection stores result rows into their owners' buffers
+    ep_tables: tuple = None
     _plan: object = field(default=None, repr=False)
     _forward: object = field(default=None, repr=False)
     _op_args: tuple = field(default=None, repr=False)
@@ -99,7 +103,8 @@ class PreparedMoE:
         # the tensors reference moe.py:151-155 counts, plus this implementation's scratch
         return sum(t.numel() * t.element_size() for t in
                    (self.counts, self.offsets, self.cursors, self.tasks, self.mapping, self.grouped_input,
-                    self.projected, self.activated, self.down_output, self.status, self.scratch))
+                    self.projected, self.activated, self.down_output, self.status, self.scratch)
+                   ) + (self.source_rows.numel() * 4 if self.source_rows is not None else 0)
 
     def check_inputs(self):
         flags = int(self.status.item())
@@ -142,6 +147,8 @@ class PreparedMoE:
                                    self.down_scales, self.valid_routes, self.residual) if t is not None]
             workspace = [self.counts, self.offsets, self.cursors, self.tasks, self.mapping, self.ranks,
                          self.grouped_input, self.activated, self.down_output, self.status, self.scratch]
+            if self.source_rows is not None:
+                workspace.append(self.source_rows)
             self._op_args = (self._plan.value, self.x, weights, self.ids, self.routing_weights, self.output, workspace)
             _ops.register_plan(self)
         _ops.forward(*self._op_args)
@@ -216,11 +223,13 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
              route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None,
-             router_bf16_weights=False, residual=None, unchained=False):
+             router_bf16_weights=False, residual=None, unchained=False, keep_grouped_input=False):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
-    W4G128 int32 word tensor instead of a BF16 tensor.
+    W4G128 int32 word tensor instead of a BF16 tensor. Unless ``keep_grouped_input`` is set, a plan whose
+    gate/up kernel can gather token rows itself does not materialise ``grouped_input`` (it stays an empty
+    tensor): the dispatch then writes ``source_rows`` (grouped row -> token) instead of copying rows.
     """
     e, h, intermediate = _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales,
                                    down_scales, route_only_experts)
@@ -242,7 +251,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           schedule=_SCHEDULES[schedule], token_tile=int(token_tile),
                           use_router=int(router_weight is not None),
                           route_only=0 if route_only_experts is None else (1 if copy_rows else 2),
-                          router_bf16_weights=int(bool(router_bf16_weights)), unchained=int(bool(unchained)))
+                          router_bf16_weights=int(bool(router_bf16_weights)), unchained=int(bool(unchained)),
+                          fused_gather=int(not keep_grouped_input))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -256,13 +266,14 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         plan = PreparedMoE(
             x, gate_up, down, ids, routing_weights, bf16((tokens, h)),
             int32((e,)), int32((e,)), int32((e,)), int32((e + 1,)), int32((r,)),
-            bf16((r, h)), bf16((0, 2 * intermediate)),
+            bf16((0 if sizes.gathers else r, h)), bf16((0, 2 * intermediate)),
             bf16((0 if route_only_experts is not None else r, intermediate)), bf16((r, h)),
             int32((1,)), config,
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
             kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
-            valid_routes=valid_routes, residual=residual)
+            valid_routes=valid_routes, residual=residual, gathers=bool(sizes.gathers),
+            source_rows=int32((r,)) if sizes.gathers else None)
         for name, tensor in (workspace or {}).items():  # caller-provided workspace (peer-visible buffers)
             if tuple(tensor.shape) != tuple(getattr(plan, name).shape) or tensor.dtype != getattr(plan, name).dtype:
                 raise ValueError(f"workspace override {name} has the wrong shape or dtype")
@@ -274,11 +285,13 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
         for name, tensor in expected.items():
             if tensor.numel() * tensor.element_size() < getattr(sizes, name):
                 raise RuntimeError(f"workspace buffer {name} smaller than the library requires")
+        if sizes.gathers and plan.source_rows.numel() * 4 < sizes.source_rows:
+            raise RuntimeError("workspace buffer source_rows smaller than the library requires")
         ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
         buffers = _native.Buffers(
             x=ptr(x), router_weight=ptr(router_weight), gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales),
             down=ptr(down), down_scales=ptr(down_scales), ids=ptr(ids), routing_weights=ptr(routing_weights),
-            valid_routes=ptr(valid_routes), residual=ptr(residual),
+            valid_routes=ptr(valid_routes), residual=ptr(residual), source_rows=ptr(plan.source_rows),
             **{name: ptr(tensor) for name, tensor in expected.items()})
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
@@ -299,21 +312,28 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
 
 
 def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0,
-                router_bf16_weights=False, residual=None):
+                router_bf16_weights=False, residual=None, keep_grouped_input=False):
     """Drop-in for reference ``prepare_moe`` (moe.py:220-245). ``router_bf16_weights`` makes the router round
     its weights through BF16 like the captured model does (scripts/capture_qwen3_moe_layer0.py:587-588).
     ``residual`` ([T,H] bf16, read every forward) is added to the layer result inside the combine kernel:
-    ``output = bf16(residual + bf16(layer))``, the model's residual add without a round trip through HBM."""
+    ``output = bf16(residual + bf16(layer))``, the model's residual add without a round trip through HBM.
+    ``keep_grouped_input=True`` makes every forward fill the ``grouped_input`` workspace tensor as the reference's
+    dispatch does; by default the gate/up kernel reads the token rows through ``source_rows`` where it can."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
-                    token_tile=token_tile, router_bf16_weights=router_bf16_weights, residual=residual)
+                    token_tile=token_tile, router_bf16_weights=router_bf16_weights, residual=residual,
+                    keep_grouped_input=keep_grouped_input)
 
 
-def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None):
+def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None,
+                         row_dest=None, return_bases=None):
     """Plan for the expert-owning side of expert parallelism: rows arrive already grouped by expert in
     ``grouped_input`` ([capacity,H], written by other ranks) and counts / offsets / tasks are written by the
     exchange kernels; the plan runs gate_up + down only (``launches[2]`` and ``launches[3]``). The exchange also
     zeroes the plan's chain words (``plan.chain``: address and count) every forward, which lets the two BF16
-    GEMM kernels overlap as they do in an ordinary plan."""
+    GEMM kernels overlap as they do in an ordinary plan. ``row_dest`` ([capacity] int32, written by the senders)
+    and ``return_bases`` (int64 device tensor, one address per rank) make the down projection store every result
+    row straight into its token owner's buffer; ``plan.fused_return`` says whether the plan took them (BF16
+    tensor-core schedule only)."""
     capacity, h = grouped_input.shape
     device = grouped_input.device
     dummy_x = grouped_input  # only shapes are taken from it
@@ -346,6 +366,11 @@ def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_sc
             status=ptr(plan.status))
         plan.scratch = int32((max(1, sizes.scratch // 4),))
         buffers.scratch = ptr(plan.scratch)
+        plan.fused_return = (row_dest is not None and return_bases is not None and down_scales is None
+                             and sizes.schedule == _native.SCHEDULE_TCGEN05)
+        if plan.fused_return:
+            buffers.ep_row_dest, buffers.ep_return_bases = ptr(row_dest), ptr(return_bases)
+            plan.ep_tables = (row_dest, return_bases)   # keep alive
         with torch.cuda.device(device):
             _native.check(lib.b200moe_plan_bind(handle, ctypes.byref(buffers)))
         first, words = ctypes.c_void_p(), ctypes.c_int32()

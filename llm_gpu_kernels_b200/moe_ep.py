@@ -289,7 +289,7 @@ class PeerExpertParallelMoE:
         self.capacity = capacity if capacity is not None else max(1, routes * self.world)
         row_bytes = hidden * 2
         sizes = {"recv": self.capacity * row_bytes, "ret": max(1, routes) * row_bytes,
-                 "counts": self.world * experts * 4, "flags": 256}
+                 "counts": self.world * experts * 4, "flags": 256, "dest": self.capacity * 4}
         with torch.cuda.device(device):
             self.buffers = PeerBuffers(sizes, group)
         recv = self.buffers.tensor("recv", sizes["recv"], device).view(torch.bfloat16).view(self.capacity, hidden)
@@ -301,8 +301,12 @@ class PeerExpertParallelMoE:
         inter = down_local.shape[2] * (8 if down_scales is not None else 1)
         tensor_tiles = hidden % 8 == 0 and inter % 8 == 0 and hidden >= 64 and inter >= 64
         tile = token_tile_for(max(1, routes * self.world), experts, 1) if tensor_tiles else 0
+        dest = self.buffers.tensor("dest", self.capacity * 4, device).view(torch.int32)
+        self.return_bases = torch.tensor(self.buffers.ptrs["ret"] + [0] * (_native.EP_MAX_RANKS - self.world),
+                                         dtype=torch.int64, device=device)
         self.expert_plan = _prepare_expert_side(gate_up_local, down_local, recv, token_tile=tile,
-                                                gate_up_scales=gate_up_scales, down_scales=down_scales)
+                                                gate_up_scales=gate_up_scales, down_scales=down_scales,
+                                                row_dest=dest, return_bases=self.return_bases)
         self.expert_rows = torch.zeros((1,), dtype=torch.int32, device=device)
         self.tables = torch.zeros((int(self.lib.b200moe_ep_table_ints(self.world, experts)),), dtype=torch.int32,
                                   device=device)
@@ -316,9 +320,10 @@ class PeerExpertParallelMoE:
                               expert_rows=ptr(self.expert_rows), expert_output=ptr(ep.down_output),
                               tables=ptr(self.tables), status=ptr(tp.status),
                               expert_chain=ctypes.c_void_p(ep.chain[0]), expert_chain_words=ep.chain[1],
-                              expert_status=ptr(ep.status))
+                              expert_status=ptr(ep.status), mapping=ptr(tp.mapping),
+                              fused_return=int(ep.fused_return))
         for field, name in (("recv_rows_peers", "recv"), ("return_rows_peers", "ret"),
-                            ("all_counts_peers", "counts"), ("flags_peers", "flags")):
+                            ("all_counts_peers", "counts"), ("flags_peers", "flags"), ("row_dest_peers", "dest")):
             array = getattr(args, field)
             for g in range(self.world):
                 array[g] = self.buffers.ptrs[name][g]
@@ -336,9 +341,10 @@ class PeerExpertParallelMoE:
         check(lib.b200moe_ep_exchange_counts(args, stream))
         check(lib.b200moe_ep_send_rows(args, stream))
         # gate/up + SwiGLU and down over the received rows, as one forward of the expert plan: the two kernels are
-        # then chained through the completion counters that the count exchange zeroed
+        # chained through the completion counters that the count exchange zeroed, and (BF16 tensor-core schedule)
+        # the down projection stores every result row straight into its token owner's buffer over NVLink
         check(ep._forward(ep._plan, stream))
-        check(lib.b200moe_ep_return_rows(args, stream))
+        check(lib.b200moe_ep_return_rows(args, stream))   # fused return: only the closing barrier
         tp.combine()
         return tp.output
 

@@ -27,7 +27,7 @@ def _check_format(packed, what):
 
 
 def prepare_w4_moe(x, packed, down, ids, routing_weights, *, down_config=None, packed_down=None,
-                   router_weight=None):
+                   router_weight=None, keep_grouped_input=False):
     """Prepare outside timing; no dense weight reconstruction, no counts read-back.
 
     ``down`` is the BF16 ``[E,H,I]`` tensor, or ``None`` when ``packed_down`` is given.
@@ -50,6 +50,7 @@ def prepare_w4_moe(x, packed, down, ids, routing_weights, *, down_config=None, p
     base = _prepare(
         x, packed.words, down if packed_down is None else packed_down.words, ids, routing_weights,
         router_weight=router_weight, schedule="tcgen05", token_tile=token_tile, config=down_config,
-        gate_up_scales=packed.scales, down_scales=None if packed_down is None else packed_down.scales)
+        gate_up_scales=packed.scales, down_scales=None if packed_down is None else packed_down.scales,
+        keep_grouped_input=keep_grouped_input)
     base.packed = packed
     return _ranked(base)

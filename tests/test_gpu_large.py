@@ -43,8 +43,13 @@ def check_dispatch(base, x_cpu, ids_cpu, experts):
     assert torch.equal(base.offsets.cpu(), offsets), "offsets"
     assert torch.equal(base.ranks.cpu(), ranks), "ranks"
     assert torch.equal(base.mapping.cpu(), mapping), "mapping"
-    gathered = base.grouped_input.cpu()[mapping.long()]
-    assert torch.equal(gathered, x_cpu.repeat_interleave(ids_cpu.shape[1], 0)), "grouped_input"
+    topk = ids_cpu.shape[1]
+    if base.gathers:   # no expert-contiguous copy: source_rows is the inverse permutation the gate/up kernel reads
+        q = torch.arange(mapping.numel())
+        assert torch.equal(base.source_rows.cpu()[mapping.long()], (q // topk).to(torch.int32)), "source_rows"
+    else:
+        gathered = base.grouped_input.cpu()[mapping.long()]
+        assert torch.equal(gathered, x_cpu.repeat_interleave(topk, 0)), "grouped_input"
     return counts
 
 
@@ -113,7 +118,7 @@ def test_qwen_skewed_routing_8192(dev, qwen, skew_case):
     _, gate_up_d, down_d = qwen["gpu"]
     x, ids, rw = skew_case
     p = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev))
-    assert p.base.token_tile == 128
+    assert p.base.token_tile == 128 and p.base.gathers
     out = p.run()
     torch.cuda.synchronize()
     p.check_inputs()
@@ -124,6 +129,10 @@ def test_qwen_skewed_routing_8192(dev, qwen, skew_case):
     print(f"zipf T=8192 max/mean rows {int(counts.max()) / mean:.1f} empty {int((counts == 0).sum())} "
           f"rel_rms={m['relative_rms']:.2e}")
     assert torch.equal(p.run(), out)
+    # the reference's materialised dispatch gives the same bits
+    kept = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev), keep_grouped_input=True)
+    assert not kept.base.gathers and torch.equal(kept.run(), out)
+    check_dispatch(kept.base, x, ids, 128)
 
 
 def test_qwen_skewed_routing_8192_w4(dev, qwen, skew_case):

@@ -44,7 +44,12 @@ def check_dispatch(base, x_cpu, ids_cpu, experts):
     assert torch.equal(base.ranks.cpu(), ranks), "ranks"
     assert torch.equal(base.mapping.cpu(), mapping), "mapping"
     topk = ids_cpu.shape[1]
-    if mapping.numel() and (mapping >= 0).all():
+    if base.gathers:   # no expert-contiguous copy: source_rows is the inverse permutation the gate/up kernel reads
+        assert base.grouped_input.numel() == 0
+        valid = mapping >= 0
+        q = torch.arange(mapping.numel())[valid]
+        assert torch.equal(base.source_rows.cpu()[mapping[valid].long()], (q // topk).to(torch.int32)), "source_rows"
+    elif mapping.numel() and (mapping >= 0).all():
         gathered = base.grouped_input.cpu()[mapping.long()]
         assert torch.equal(gathered, x_cpu.repeat_interleave(topk, 0)), "grouped_input"
 
@@ -88,17 +93,22 @@ TC = [
 ]
 
 
+@pytest.mark.parametrize("keep", [False, True])
 @pytest.mark.parametrize("t,e,k,h,i,pattern,tile", TC)
-def test_tcgen05_small_shapes(dev, t, e, k, h, i, pattern, tile):
+def test_tcgen05_small_shapes(dev, t, e, k, h, i, pattern, tile, keep):
+    """keep=False: the gate/up kernel gathers the token rows itself (no grouped_input); keep=True: the dispatch
+    materialises grouped_input as the reference does. Same bits either way."""
     cpu = make_inputs(t, e, k, h, i, pattern=pattern, seed=100 + t, wscale=0.1, signed=True)
     gpu = tuple(a.to(dev) for a in cpu)
-    p = prep()(*gpu, schedule="tcgen05", token_tile=tile)
-    assert p.base.schedule == "tcgen05"
+    p = prep()(*gpu, schedule="tcgen05", token_tile=tile, keep_grouped_input=keep)
+    assert p.base.schedule == "tcgen05" and p.base.gathers == (not keep)
     out = p.run()
     torch.cuda.synchronize()
     p.check_inputs()
     check_dispatch(p.base, cpu[0], cpu[3], e)
     check_output(out, cpu)
+    if not keep:   # gathered and materialised rows give the same bits
+        assert torch.equal(prep()(*gpu, schedule="tcgen05", token_tile=tile, keep_grouped_input=True).run(), out)
     # same inputs through the CUDA-core schedule agree as well (two independent kernels)
     q = prep()(*gpu, schedule="generic")
     m = O.error_metrics(out.float().cpu(), q.run().float().cpu())
@@ -273,7 +283,7 @@ def test_empty_tokens(dev):
 def test_workspace_contract(dev):
     """Buffers are distinct storages, owned by the plan (reference moe_benchmark.py:193-206)."""
     args = make_inputs(9, 8, 2, 128, 64, device=dev)
-    p = prep()(*args)
+    p = prep()(*args, keep_grouped_input=True)
     b = p.base
     names = ("output", "counts", "offsets", "cursors", "tasks", "mapping", "grouped_input", "projected",
              "activated", "down_output", "status")

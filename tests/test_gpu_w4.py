@@ -76,6 +76,11 @@ def test_w4_small_shapes(dev, t, e, k, h, i, both, tile):
     p.check_inputs()
     check(out, x, dequantize_gate_up_reference(pg), dequantize_gate_up_reference(pd) if both else down, ids, rw)
     assert torch.equal(p.run(), out)
+    assert p.base.gathers == (p.base.token_tile <= 16)
+    if p.base.gathers:   # the materialised dispatch gives the same bits
+        kept = prepare_w4_moe(x.to(dev), pg.to(dev), None if both else down.to(dev), ids.to(dev), rw.to(dev),
+                              packed_down=pd.to(dev) if both else None, down_config=cfg, keep_grouped_input=True)
+        assert not kept.base.gathers and torch.equal(kept.run(), out)
 
 
 @pytest.fixture(scope="module")

@@ -63,7 +63,7 @@ def test_static_dispatch_matches_regular_dispatch_twice(tokens, experts, topk, h
     lib = _native.load()
     x, gate_up, down, ids, rw = make_inputs(tokens, experts, topk, hidden, 64, seed=5, id_dtype=id_dtype,
                                             device=dev, wscale=0.1)
-    regular = prepare_moe(x, gate_up, down, ids, rw)
+    regular = prepare_moe(x, gate_up, down, ids, rw, keep_grouped_input=True)
     routes = tokens * topk
     i32 = lambda n: torch.full((n,), -12345, dtype=torch.int32, device=dev)
     out = dict(counts=i32(experts), offsets=i32(experts), cursors=i32(experts), tasks=i32(experts + 1),
