@@ -113,34 +113,10 @@ __device__ __forceinline__ bool wait_expert_done(const int* done, int need, int*
 // (gate columns at taddr, up columns at taddr + token_tile). kSumPair: the tile was accumulated as two partial
 // sums over K (even and odd K steps, by two MMA-issuing threads) in the same two column ranges; they are added
 // here, in FP32. The whole warp must call it.
-// row_dest / ret_bases (expert-parallel expert plans, else null): row r of the result belongs to another rank - it is
-// stored at row (row_dest[r] & 0xFFFFFF) of the buffer ret_bases[row_dest[r] >> 24] instead of row r of `out`.
 template <bool kGateUp, bool kSumPair = false>
 __device__ __forceinline__ void store_tile(const Tile& t, uint32_t taddr, int token_tile, int channel, int n_out,
-                                           __nv_bfloat16* __restrict__ out, const int* row_dest = nullptr,
-                                           const unsigned long long* ret_bases = nullptr) {
+                                           __nv_bfloat16* __restrict__ out) {
   const bool ch_ok = channel < n_out;
-  if (row_dest != nullptr) {   // plain stores into peer memory, one 64-byte row segment per warp instruction
-    for (int n0 = 0; n0 < t.n_eff; n0 += 16) {
-      uint32_t g[16], u[16];
-      ptx::tmem_ld16(taddr + n0, g);
-      if (kGateUp || kSumPair) ptx::tmem_ld16(taddr + token_tile + n0, u);
-      ptx::tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int n = n0 + j;
-        if (n < t.rows) {   // warp-uniform
-          float v = __uint_as_float(g[j]);
-          if (kGateUp) v = (v / (1.0f + __expf(-v))) * __uint_as_float(u[j]);
-          else if (kSumPair) v = __fadd_rn(v, __uint_as_float(u[j]));
-          const int d = row_dest[t.row0 + n];
-          __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(ret_bases[static_cast<unsigned>(d) >> 24]);
-          if (ch_ok) base[static_cast<size_t>(d & 0xFFFFFF) * n_out + channel] = __float2bfloat16_rn(v);
-        }
-      }
-    }
-    return;
-  }
   __nv_bfloat16* dst = out + static_cast<size_t>(t.row0) * n_out + channel;
   for (int n0 = 0; n0 < t.n_eff; n0 += 16) {
     uint32_t g[16], u[16];

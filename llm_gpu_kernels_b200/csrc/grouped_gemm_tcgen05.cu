@@ -59,6 +59,10 @@ constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
 static_assert(kItemRing >= kMaxStages + 3, "producer could lap the item ring");
+// Staging of the epilogue that returns rows to other ranks: 16 rows x 128 channels BF16 (+16 bytes of padding per
+// row), two buffers.
+constexpr uint32_t kEpiRowBytes = kTileM * 2 + 16;
+constexpr uint32_t kEpiBufBytes = 16 * kEpiRowBytes;
 
 struct Ctrl {
   uint64_t full[kMaxStages];
@@ -66,6 +70,7 @@ struct Ctrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain[2];
+  uint64_t epi_bar[2];            // the four epilogue warps wrote their part of a staging buffer
   uint64_t item_ready[kItemRing];
   int item[kItemRing];
   uint32_t tmem_base;
@@ -74,12 +79,58 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
+// Epilogue of the down projection of an expert-parallel expert plan: result row r of the tile belongs to another
+// rank and goes to row (row_dest[r] & 0xFFFFFF) of the buffer ret_bases[row_dest[r] >> 24], over NVLink. The
+// accumulator has the channel on the TMEM lane, so a thread holds one channel of 16 rows; stored like that a warp
+// would write 64-byte pieces, which NVLink moves badly. The four epilogue warps therefore transpose 16 rows x 128
+// channels through shared memory and write whole 256-byte row segments, 16 bytes per lane. `chunk` counts the
+// 16-row chunks this warp has staged (all four warps walk the same sequence). Returns false when a wait gave up.
+__device__ __forceinline__ bool return_tile_rows(const Tile& t, uint32_t taddr, int token_tile, int quarter, int lane,
+                                                 int n_out, const int* __restrict__ row_dest,
+                                                 const unsigned long long* __restrict__ ret_bases,
+                                                 unsigned char* epi, uint64_t* epi_bar, unsigned& chunk, int* abort,
+                                                 int* status, bool pair) {
+  for (int n0 = 0; n0 < t.n_eff; n0 += 16, ++chunk) {
+    uint32_t g[16], u[16];
+    tmem_ld16(taddr + n0, g);
+    if (pair) {
+      tmem_ld16(taddr + token_tile + n0, u);   // the odd-K partial sum of the second MMA issuer
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) u[j] = 0u;
+    }
+    tmem_ld_wait();
+    const unsigned buf = chunk & 1u;
+    unsigned char* stage = epi + buf * kEpiBufBytes;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      *reinterpret_cast<__nv_bfloat16*>(stage + j * kEpiRowBytes + (quarter * 32 + lane) * 2) =
+          __float2bfloat16_rn(__fadd_rn(__uint_as_float(g[j]), __uint_as_float(u[j])));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&epi_bar[buf]);
+    if (!__all_sync(0xffffffffu, mbar_wait(&epi_bar[buf], (chunk >> 1) & 1u, abort, status))) return false;
+    // this warp sends rows quarter*4 .. quarter*4+3 of the chunk: two rows per instruction, 16 lanes x 16 bytes each
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int row = quarter * 4 + rr * 2 + (lane >> 4), n = n0 + row;
+      const int channel = t.ct * kTileM + (lane & 15) * 8;
+      if (n < t.rows && channel < n_out) {
+        const int d = row_dest[t.row0 + n];
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(ret_bases[static_cast<unsigned>(d) >> 24]);
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + row * kEpiRowBytes + (lane & 15) * 16);
+        *reinterpret_cast<uint4*>(base + static_cast<size_t>(d & 0xFFFFFF) * n_out + channel) = v;
+      }
+    }
+  }
+  return true;
+}
+
 // chain_done: per-expert completion counters of the gate/up stage (null = stages separated by kernel
 // boundaries). The gate/up kernel adds one per epilogue warp and tile; the down kernel, given
 // chain_need = arrivals per token tile of an expert, waits for them before it loads activated rows.
 // tile_counter (down kernel only): global tile counter of the dynamic schedule, zero at launch.
 // row_dest / ret_bases (down kernel of an expert-parallel expert plan, else null): the result rows are stored
-// straight into their token owners' buffers over NVLink (see store_tile).
+// straight into their token owners' buffers over NVLink (see return_tile_rows).
 // kGather (gate/up only): the rows of a tile are not read from an expert-contiguous copy but gathered from the
 // token rows themselves: source_rows[r] = token whose row grouped row r is (written by the dispatch), x = [T, k_dim].
 // Four extra warps copy 16-byte chunks with cp.async into the 128-byte-swizzled activation tile of each stage
@@ -103,7 +154,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   constexpr uint32_t kWBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;
   const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
   const uint32_t stage_bytes = kWBytes + act_bytes;
-  const int acc_cols = 2 * token_tile;   // gate and up, or the two partial sums of down
+  // At token tile 256 an MMA (N = 256) takes longer than one thread needs to issue it, so the down projection runs
+  // with ONE issuer and one partial sum: its accumulator is 256 columns and still double-buffered (the epilogue of
+  // a K = I tile is too long to leave unoverlapped). gate/up needs gate + up = 512 columns either way.
+  const bool single_issuer = !kGateUp && token_tile > 128;
+  const int acc_cols = single_issuer ? token_tile : 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(num_acc * acc_cols)) tmem_cols <<= 1;
@@ -115,15 +170,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(&c->full[s], kGather ? 1 + 32 * kGatherWarps : 1);   // TMA (+ every gather lane's copies)
-      mbar_init(&c->empty[s], 2);   // the commits of the two MMA issuers
+      mbar_init(&c->empty[s], single_issuer ? 1 : 2);   // the commits of the MMA issuers
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&c->tmem_full[a], 2);  // the two MMA issuers
+      mbar_init(&c->tmem_full[a], single_issuer ? 1 : 2);  // the MMA issuers
       mbar_init(&c->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
     for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
     mbar_init(&c->drain[0], 1);
     mbar_init(&c->drain[1], 1);
+    mbar_init(&c->epi_bar[0], 4);
+    mbar_init(&c->epi_bar[1], 4);
     c->abort = 0;
     mbar_init_fence();
   }
@@ -188,7 +245,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       }
     }
   } else if (warp == 1 || warp == kMmaWarpB) {
-    if (lane == 0) {
+    if (lane == 0 && !(single_issuer && warp == kMmaWarpB)) {
       // ---------------------------------------------------------------- MMA issuers (0: gate / even K, 1: up / odd K)
       const int half = warp == 1 ? 0 : 1;
       int stage = 0, acc = 0;
@@ -215,6 +272,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             if (kGateUp) {
               umma(half ? d_up : d_gate, umma_desc(w_addr + half * kWTileBytes + k * kUmmaK * 2), bdesc, idesc,
                    (kb | k) != 0 ? 1u : 0u);
+            } else if (single_issuer) {
+              umma(d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
             } else if ((k & 1) == half) {
               umma(half ? d_up : d_gate, umma_desc(w_addr + k * kUmmaK * 2), bdesc, idesc, (kb | (k >> 1)) != 0 ? 1u : 0u);
             }
@@ -277,6 +336,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    unsigned epi_chunk = 0;
+    unsigned char* epi = stages + static_cast<size_t>(num_stages) * stage_bytes;   // reserved when row_dest is set
     for (int seq = 0;; ++seq) {
       // warp-uniform outcomes: the TMEM loads below need the whole warp
       const int item = follow_item(c, dynamic, seq, total_items, status);
@@ -285,8 +346,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out,
-                                    kGateUp ? nullptr : row_dest, ret_bases);
+      if (!kGateUp && row_dest != nullptr) {
+        if (!return_tile_rows(t, taddr, token_tile, quarter, lane, n_out, row_dest, ret_bases, epi, c->epi_bar,
+                              epi_chunk, &c->abort, status, !single_issuer))
+          break;
+      } else if (single_issuer) {
+        store_tile<false, false>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      } else {
+        store_tile<kGateUp, !kGateUp>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
+      }
       tc_fence_before();
       if (kGateUp && chain_done != nullptr) {
         // this lane's rows were written through the generic proxy and the down kernel reads them through the
@@ -312,11 +380,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   }
 }
 
-int stages_for(bool gate_up, int token_tile, int* smem_bytes) {
+int stages_for(bool gate_up, int token_tile, int* smem_bytes, int reserve = 0) {
   const int stage = (gate_up ? 2 : 1) * static_cast<int>(kWTileBytes) + token_tile * 128;
-  int stages = (kSmemLimit - kCtrlBytes - 1024) / stage;
+  int stages = (kSmemLimit - kCtrlBytes - 1024 - reserve) / stage;
   if (stages > kMaxStages) stages = kMaxStages;
-  *smem_bytes = kCtrlBytes + 1024 + stages * stage;
+  *smem_bytes = kCtrlBytes + 1024 + stages * stage + reserve;
   return stages;
 }
 
@@ -351,7 +419,8 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
 
 int configure_tc(B200MoePlan& p) {
   p.gemm_stages_gate_up = stages_for(true, p.token_tile, &p.gemm_smem_gate_up);
-  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down);
+  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down,
+                                  p.buf.ep_row_dest ? 2 * static_cast<int>(kEpiBufBytes) : 0);
   if (p.gemm_stages_gate_up < 2 || p.gemm_stages_down < 2) {
     set_error("token_tile %d leaves fewer than 2 shared-memory stages", p.token_tile);
     return B200MOE_ERR_INVALID;
