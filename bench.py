@@ -761,15 +761,20 @@ def main_ep(args, dev, peaks, rank, world):
             configs["copy_probe"] = copy_probe(dev, timer, args.tokens * h * 2, rank, world)
         del full, local
         torch.cuda.empty_cache()
-        if world == 8 and not args.only_headline:
-            # BASELINE config 5: Mixtral-8x7B layer shape, T=32768, one expert per GPU. Every rank draws only its
-            # own expert's weights; rank 0 redraws the experts its sampled tokens use for the oracle check.
+        if MIXTRAL["experts"] % world == 0 and not args.only_headline:
+            # BASELINE config 5: Mixtral-8x7B layer shape, T=32768 over all ranks, 8/N experts per GPU (one expert per
+            # GPU at N=8). Every rank draws only its own experts' weights, each from a seed of its own; rank 0
+            # redraws the experts its sampled tokens use for the oracle check.
             m = MIXTRAL
-            wr_m, gu1, dn1, _ = seeded_weights(only_expert=rank, **m)
+            mlo, mhi = expert_range(rank, world, m["experts"])
+            drawn = [seeded_weights(only_expert=expert, **m) for expert in range(mlo, mhi)]
+            wr_m = drawn[0][0]
+            gu_m = torch.cat([d[1] for d in drawn]).to(dev)
+            dn_m = torch.cat([d[2] for d in drawn]).to(dev)
+            del drawn
             t_rank = 32768 // world
             x_m = torch.randn(t_rank, m["hidden"], generator=torch.Generator().manual_seed(2000 + rank)).bfloat16()
-            configs["mixtral_T32768"] = mixtral_case(m, t_rank, x_m, (gu1.to(dev), dn1.to(dev)), wr_m, dev, timer,
-                                                     rank, world, peaks)
+            configs["mixtral_T32768"] = mixtral_case(m, t_rank, x_m, (gu_m, dn_m), wr_m, dev, timer, rank, world, peaks)
     if rank == 0:
         ms = head["ms"]
         line = {
@@ -806,7 +811,7 @@ def main_ep(args, dev, peaks, rank, world):
 
 
 def mixtral_case(m, tokens, x_host, local_weights, wr, dev, timer, rank, world, peaks):
-    """One expert per GPU at the Mixtral shape. No rank holds all experts, so the check is the FP32 oracle on a
+    """8/N experts per GPU at the Mixtral shape. No rank holds all experts, so the check is the FP32 oracle on a
     few sampled tokens of rank 0, whose experts' weights rank 0 redraws from their seeds on the host."""
     from llm_gpu_kernels_b200.moe_ep import prepare_peer_ep_moe
     dist = torch.distributed
@@ -857,8 +862,8 @@ def mixtral_case(m, tokens, x_host, local_weights, wr, dev, timer, rank, world, 
     status = int(ep.token_plan.status.item()) | int(ep.expert_plan.status.item())
     dist.barrier()
     ep.close()
-    return {"workload": "Mixtral-8x7B layer shape E8 H4096 I14336 top-2, T=32768 over 8 GPUs (4096 tokens and one "
-                        "expert per GPU), device router", "ms": ms, "windows": windows,
+    return {"workload": f"Mixtral-8x7B layer shape E8 H4096 I14336 top-2, T=32768 over {world} GPUs ({tokens} tokens and "
+                        f"{e // world} expert(s) per GPU), device router", "ms": ms, "windows": windows,
             "tokens_per_s": world * tokens / (ms * 1e-3), "rows_received_max": rows_max, "rows_received_mean": rows_mean,
             "rows_max_over_mean": rows_max / max(rows_mean, 1.0), "status": status,
             "token_tile": ep.expert_plan.token_tile, "parity": parity,

@@ -93,7 +93,10 @@ def test_one_rank_expert_parallel(shape):
     assert result[0][1] == shape[0] * shape[2]
 
 
-@pytest.mark.parametrize("shape", [(96, 16, 4, 256, 128, True), (1024, 128, 8, 2048, 768, True)])
+# the last shape: one expert per rank with 4096 rows each, i.e. token tile 256 on the expert side (one MMA issuer,
+# rows returned from the down epilogue without a second partial sum)
+@pytest.mark.parametrize("shape", [(96, 16, 4, 256, 128, True), (1024, 128, 8, 2048, 768, True),
+                                   (2048, 2, 2, 512, 1024, True)])
 def test_two_rank_expert_parallel(shape):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
