@@ -28,6 +28,7 @@
 #include "sm100_ptx.cuh"
 #include "gemm_tile.cuh"
 #include "pdl.cuh"
+#include "w4_dequant.cuh"
 
 namespace b200moe {
 namespace {
@@ -61,25 +62,6 @@ struct Ctrl {
   Tables tables;
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
-
-// Eight nibbles of one word -> eight BF16 in K order, scaled: one 16-byte chunk of the operand row.
-__device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 scale2) {
-  const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
-  uint32_t pair[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + n_j, 128 + n_(j+4)}
-    __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
-    q = __hmul2(q, scale2);
-    pair[j] = *reinterpret_cast<uint32_t*>(&q);
-  }
-  uint4 out;
-  out.x = __byte_perm(pair[0], pair[1], 0x5410);  // k0 k1
-  out.y = __byte_perm(pair[2], pair[3], 0x5410);  // k2 k3
-  out.z = __byte_perm(pair[0], pair[1], 0x7632);  // k4 k5
-  out.w = __byte_perm(pair[2], pair[3], 0x7632);  // k6 k7
-  return out;
-}
 
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -284,6 +266,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
     // gate/up: part&1 picks the gate or up tile, part>>1 the 16-byte half of the row's 32 bytes per 64 K
     //          (four words each); down: part picks a quarter of the row's 32 bytes (two words each).
     const int half = kGateUp ? (part & 1) : 0;
+    const w4::Consts k4 = w4::make_consts();
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
     int p = 0, q = 0;
     uint32_t pph = 0, qph = 0;
@@ -318,12 +301,12 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_words, const __gri
             const uint32_t w[4] = {w0.x, w0.y, w0.z, w0.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(dst + (((ch * 4 + i) ^ (row & 7)) << 4)) = dequant_word(w[i], scale2);
+              *reinterpret_cast<uint4*>(dst + (((ch * 4 + i) ^ (row & 7)) << 4)) = w4::dequant_word(w[i], scale2, k4);
           } else {
             const uint2 w0 = *reinterpret_cast<const uint2*>(words + (((2 * j + (part >> 1)) ^ (row & 7)) << 4) +
                                                              (part & 1) * 8);
-            *reinterpret_cast<uint4*>(dst + (((part * 2) ^ (row & 7)) << 4)) = dequant_word(w0.x, scale2);
-            *reinterpret_cast<uint4*>(dst + (((part * 2 + 1) ^ (row & 7)) << 4)) = dequant_word(w0.y, scale2);
+            *reinterpret_cast<uint4*>(dst + (((part * 2) ^ (row & 7)) << 4)) = w4::dequant_word(w0.x, scale2, k4);
+            *reinterpret_cast<uint4*>(dst + (((part * 2 + 1) ^ (row & 7)) << 4)) = w4::dequant_word(w0.y, scale2, k4);
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
           __syncwarp();

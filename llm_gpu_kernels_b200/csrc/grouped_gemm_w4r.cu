@@ -38,6 +38,7 @@
 #include "sm100_ptx.cuh"
 #include "gemm_tile.cuh"
 #include "pdl.cuh"
+#include "w4_dequant.cuh"
 
 namespace b200moe {
 namespace {
@@ -95,34 +96,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// (a & b) | c in ONE logic instruction. Left to itself the compiler keeps both constants as immediates and spends
-// two instructions per nibble pair; with the constants in registers the three-input form takes one.
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-
-// One packed word -> four BF16 pairs {k_j, k_(j+4)}, j = 0..3, each bf16_rn(q * scale).
-// mask = 0x000F000F and magic = 0x43004300 come in as registers the compiler cannot see through.
-__device__ __forceinline__ void dequant_pairs(uint32_t w, __nv_bfloat162 scale2, uint32_t mask, uint32_t magic,
-                                              uint32_t (&pair)[4]) {
-  const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t v = and_or(w >> (4 * j), mask, magic);   // {128 + n_j, 128 + n_(j+4)}
-    __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);   // exact
-    q = __hmul2(q, scale2);                                                       // the one rounding
-    pair[j] = *reinterpret_cast<uint32_t*>(&q);
-  }
-}
-
 // One consumer warp's share of one stage: 128 K (four 32-K chunks) of its 16 channel rows in both weight boxes,
 // against kNT column tiles of 8 rows. w_base: the stage; b_base: the activation tile at this thread's row g.
 template <int kNT>
 __device__ __forceinline__ void multiply_half(float (&acc)[2][kMaxNT][4], uint32_t w_base, uint32_t b_base,
                                               const __nv_bfloat162 (&sc)[2][2], int group, uint32_t lm_row,
-                                              uint32_t lm_chunk, int t4, int g, uint32_t mask, uint32_t magic) {
+                                              uint32_t lm_chunk, int t4, int g, const w4::Consts& k4) {
   // all packed words of this stage half first: the loads overlap the arithmetic of the chunks before
   uint32_t wl[2][4], wh[2][4];
 #pragma unroll
@@ -143,10 +122,10 @@ __device__ __forceinline__ void multiply_half(float (&acc)[2][kMaxNT][4], uint32
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) b[nt] = lds128(b_base + nt * 8 * kRowBytes + b_off);
       uint32_t a[2][2][4];   // [box][row g / g+8][pair]
-      dequant_pairs(wl[c2l][2 * cc], sc[0][0], mask, magic, a[0][0]);
-      dequant_pairs(wl[c2l][2 * cc + 1], sc[0][1], mask, magic, a[0][1]);
-      dequant_pairs(wh[c2l][2 * cc], sc[1][0], mask, magic, a[1][0]);
-      dequant_pairs(wh[c2l][2 * cc + 1], sc[1][1], mask, magic, a[1][1]);
+      w4::dequant_pairs(wl[c2l][2 * cc], sc[0][0], k4, a[0][0]);
+      w4::dequant_pairs(wl[c2l][2 * cc + 1], sc[0][1], k4, a[0][1]);
+      w4::dequant_pairs(wh[c2l][2 * cc], sc[1][0], k4, a[1][0]);
+      w4::dequant_pairs(wh[c2l][2 * cc + 1], sc[1][1], k4, a[1][1]);
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) {
 #pragma unroll
@@ -314,8 +293,7 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
     // for two consecutive 16-byte chunks (32 K each) of the 128-byte row
     const uint32_t lm_row = static_cast<uint32_t>(blk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7));
     const uint32_t lm_chunk = static_cast<uint32_t>(lane >> 4);
-    uint32_t mask = 0x000F000Fu, magic = 0x43004300u;   // made opaque once: see and_or()
-    asm volatile("" : "+r"(mask), "+r"(magic));
+    const w4::Consts k4 = w4::make_consts();
     bool ok = true;
     for (int seq = 0; ok; ++seq) {
       const int item = follow_item(c, dynamic, seq, total_items, status);
@@ -364,8 +342,8 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
           const uint32_t w_base = smem_u32(stages + static_cast<size_t>(stage) * stage_bytes);
           const uint32_t b_base = w_base + 2 * kBoxBytes + static_cast<uint32_t>(g) * kRowBytes;
           if (k_left > 0) {   // K is a multiple of 128: a stage half is whole or absent
-            if (n_tiles == 1) multiply_half<1>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, mask, magic);
-            else multiply_half<2>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, mask, magic);
+            if (n_tiles == 1) multiply_half<1>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, k4);
+            else multiply_half<2>(acc, w_base, b_base, sc, group, lm_row, lm_chunk, t4, g, k4);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&c->empty[stage]);

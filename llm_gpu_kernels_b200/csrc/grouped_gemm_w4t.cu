@@ -31,6 +31,7 @@
 #include "sm100_ptx.cuh"
 #include "gemm_tile.cuh"
 #include "pdl.cuh"
+#include "w4_dequant.cuh"
 
 namespace b200moe {
 namespace {
@@ -65,25 +66,6 @@ struct Ctrl {
   Tables tables;
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
-
-// Eight nibbles of one word -> eight BF16 in K order, scaled: one 16-byte chunk of the operand row.
-__device__ __forceinline__ uint4 dequant_word_t(uint32_t w, __nv_bfloat162 scale2) {
-  const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);  // 128 (magic exponent) + 8 (zero point)
-  uint32_t pair[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + n_j, 128 + n_(j+4)}
-    __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
-    q = __hmul2(q, scale2);
-    pair[j] = *reinterpret_cast<uint32_t*>(&q);
-  }
-  uint4 out;
-  out.x = __byte_perm(pair[0], pair[1], 0x5410);  // k0 k1
-  out.y = __byte_perm(pair[2], pair[3], 0x5410);  // k2 k3
-  out.z = __byte_perm(pair[0], pair[1], 0x7632);  // k4 k5
-  out.w = __byte_perm(pair[2], pair[3], 0x7632);  // k6 k7
-  return out;
-}
 
 // chain_done / chain_need / tile_counter: as in the BF16 kernel (grouped_gemm_tcgen05.cu). The gate/up kernel adds
 // one to chain_done[expert] per epilogue warp and tile; the down kernel, launched as a programmatic dependent, does
@@ -298,6 +280,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // channel row of the tile = TMEM lane
     const int part = (warp - 6) >> 2;             // 0..3: the sub-block of each words stage this warp converts
+    const w4::Consts k4 = w4::make_consts();
     const long long total_rows = static_cast<long long>(E) * w_rows_per_expert;
     int p = 0, gst = 0;                           // words slot; operand stages so far (all warps count)
     uint32_t pph = 0;
@@ -340,7 +323,7 @@ grouped_gemm_w4t_kernel(const __grid_constant__ CUtensorMap tm_words, const __gr
             uint32_t r[16];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 d = dequant_word_t(ww[i], scale2);
+              const uint4 d = w4::dequant_word(ww[i], scale2, k4);
               r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
             }
             // gate columns [0,64) and up columns [64,128) of the stage (down: [0,64)), this warp's 64-K half
