@@ -641,7 +641,9 @@ def ep_case(name, shape, tokens, x_host, local_weights, wr, routes, dev, timer, 
                            "note": "slowest rank: max(weights + activations over HBM, 6*rows*H*I over the "
                                    "sustained BF16 peak) + 2*rows*H*2*(N-1)/N bytes over one NVLink direction"}}
     if mode == "peer":
-        result["launches"] = token_plan.kernel_launches + 1 + 2 + 2 + 2 + 1
+        # router + dispatch, count exchange, send + barrier, gate/up, down, (return copy unless the down epilogue
+        # returns the rows), closing barrier, combine
+        result["launches"] = token_plan.kernel_launches + 1 + 2 + 2 + (0 if expert_plan.fused_return else 1) + 1 + 1
     else:
         result["launches"] = token_plan.kernel_launches + 1 + expert_plan.kernel_launches
 
