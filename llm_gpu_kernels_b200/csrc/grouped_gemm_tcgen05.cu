@@ -84,12 +84,13 @@ static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 // accumulator has the channel on the TMEM lane, so a thread holds one channel of 16 rows; stored like that a warp
 // would write 64-byte pieces, which NVLink moves badly. The four epilogue warps therefore transpose 16 rows x 128
 // channels through shared memory and write whole 256-byte row segments, 16 bytes per lane. `chunk` counts the
-// 16-row chunks this warp has staged (all four warps walk the same sequence). Returns false when a wait gave up.
+// 16-row chunks this warp has staged (all four warps walk the same sequence); channel0 = first of the 128 channels
+// behind `taddr`. Returns false when a wait gave up.
 __device__ __forceinline__ bool return_tile_rows(const Tile& t, uint32_t taddr, int token_tile, int quarter, int lane,
                                                  int n_out, const int* __restrict__ row_dest,
                                                  const unsigned long long* __restrict__ ret_bases,
                                                  unsigned char* epi, uint64_t* epi_bar, unsigned& chunk, int* abort,
-                                                 int* status, bool pair) {
+                                                 int* status, bool pair, int channel0) {
   for (int n0 = 0; n0 < t.n_eff; n0 += 16, ++chunk) {
     uint32_t g[16], u[16];
     tmem_ld16(taddr + n0, g);
@@ -113,7 +114,7 @@ __device__ __forceinline__ bool return_tile_rows(const Tile& t, uint32_t taddr, 
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       const int row = quarter * 4 + rr * 2 + (lane >> 4), n = n0 + row;
-      const int channel = t.ct * kTileM + (lane & 15) * 8;
+      const int channel = channel0 + (lane & 15) * 8;
       if (n < t.rows && channel < n_out) {
         const int d = row_dest[t.row0 + n];
         __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(ret_bases[static_cast<unsigned>(d) >> 24]);
@@ -136,7 +137,12 @@ __device__ __forceinline__ bool return_tile_rows(const Tile& t, uint32_t taddr, 
 // Four extra warps copy 16-byte chunks with cp.async into the 128-byte-swizzled activation tile of each stage
 // (what the TMA box load would have written) and arrive on the stage's barrier through
 // cp.async.mbarrier.arrive, so the copies of several stages are in flight and no register holds data.
-template <bool kGateUp, bool kGather = false>
+// kPair (down projection only): one tile is TWO channel tiles (256 output channels) of one token tile. The two weight
+// boxes share every activation tile in shared memory, exactly as the gate and the up box do, each MMA issuer owns one
+// channel tile over all of K and there are no partial sums. Once an expert has several token tiles the kernels are
+// bound by what they pull out of L2 per FLOP (ncu at T=8192: 3.2 GB of operand tiles through L2 for the down
+// projection, 7.7 TB/s, tensor pipe 24 % busy); sharing the activation tile cuts that by a quarter.
+template <bool kGateUp, bool kGather = false, bool kPair = false>
 __global__ void __launch_bounds__(kGather ? kGatherThreads : kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_act,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ g_offsets,
@@ -146,18 +152,21 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                        const int* row_dest, const unsigned long long* ret_bases,
                        const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows) {
   static_assert(kGateUp || !kGather, "only the gate/up projection gathers token rows");
+  static_assert(!kGateUp || !kPair, "the pair tile is a schedule of the down projection");
+  constexpr bool kTwoBoxes = kGateUp || kPair;          // two weight boxes per stage, one MMA issuer each
+  constexpr int kTileChannels = kPair ? 2 * kTileM : kTileM;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t stage_off = ((raw_addr + kCtrlBytes + 1023u) & ~1023u) - raw_addr;
   unsigned char* stages = smem_raw + stage_off;
-  constexpr uint32_t kWBytes = kGateUp ? 2 * kWTileBytes : kWTileBytes;
+  constexpr uint32_t kWBytes = kTwoBoxes ? 2 * kWTileBytes : kWTileBytes;
   const uint32_t act_bytes = static_cast<uint32_t>(token_tile) * 128u;
   const uint32_t stage_bytes = kWBytes + act_bytes;
   // At token tile 256 an MMA (N = 256) takes longer than one thread needs to issue it, so the down projection runs
   // with ONE issuer and one partial sum: its accumulator is 256 columns and still double-buffered (the epilogue of
   // a K = I tile is too long to leave unoverlapped). gate/up needs gate + up = 512 columns either way.
-  const bool single_issuer = !kGateUp && token_tile > 128;
+  const bool single_issuer = !kTwoBoxes && token_tile > 128;
   const int acc_cols = single_issuer ? token_tile : 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
@@ -199,7 +208,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&c->tmem_base);
 
-  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const int n_ct = (n_out + kTileChannels - 1) / kTileChannels;
   const int num_kb = (k_dim + kBlockK - 1) / kBlockK;
   const int total_items = c->tables.tasks[E] * n_ct;
 
@@ -218,7 +227,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                                  : follow_item(c, false, seq, total_items, status);
         if (item < 0) break;
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
-        const int w_row = t.expert * w_rows_per_expert + t.ct * kTileM;
+        const int w_row = t.expert * w_rows_per_expert + t.ct * kTileChannels;
         if (chained && t.expert != ready_expert) {
           const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
           if (!wait_expert_done(chain_done + t.expert, need, &c->abort, status)) { ok = false; break; }
@@ -229,7 +238,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
           unsigned char* st = stages + static_cast<size_t>(stage) * stage_bytes;
           mbar_expect_tx(&c->full[stage], kGather ? kWBytes : stage_bytes);
           tma_load_2d(st, &tm_w, &c->full[stage], kb * kBlockK, w_row, pol_w);
-          if (kGateUp) tma_load_2d(st + kWTileBytes, &tm_w, &c->full[stage], kb * kBlockK, w_row + n_out, pol_w);
+          if (kTwoBoxes)   // the up rows of the same channels / the next 128 channels
+            tma_load_2d(st + kWTileBytes, &tm_w, &c->full[stage], kb * kBlockK, w_row + (kGateUp ? n_out : kTileM), pol_w);
           if (!kGather) tma_load_2d(st + kWBytes, &tm_act, &c->full[stage], kb * kBlockK, t.row0, pol_act);
           ++issued;
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -269,7 +279,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint64_t bdesc = umma_desc(a_addr + k * kUmmaK * 2);
-            if (kGateUp) {
+            if (kTwoBoxes) {
               umma(half ? d_up : d_gate, umma_desc(w_addr + half * kWTileBytes + k * kUmmaK * 2), bdesc, idesc,
                    (kb | k) != 0 ? 1u : 0u);
             } else if (single_issuer) {
@@ -347,9 +357,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
       if (!kGateUp && row_dest != nullptr) {
-        if (!return_tile_rows(t, taddr, token_tile, quarter, lane, n_out, row_dest, ret_bases, epi, c->epi_bar,
-                              epi_chunk, &c->abort, status, !single_issuer))
-          break;
+        bool sent = return_tile_rows(t, taddr, token_tile, quarter, lane, n_out, row_dest, ret_bases, epi, c->epi_bar,
+                                     epi_chunk, &c->abort, status, !single_issuer && !kPair, t.ct * kTileChannels);
+        if (sent && kPair)
+          sent = return_tile_rows(t, taddr + token_tile, token_tile, quarter, lane, n_out, row_dest, ret_bases, epi,
+                                  c->epi_bar, epi_chunk, &c->abort, status, false, t.ct * kTileChannels + kTileM);
+        if (!sent) break;
+      } else if (kPair) {
+        store_tile<false, false>(t, taddr, token_tile, t.ct * kTileChannels + quarter * 32 + lane, n_out, out);
+        store_tile<false, false>(t, taddr + token_tile, token_tile, t.ct * kTileChannels + kTileM + quarter * 32 + lane,
+                                 n_out, out);
       } else if (single_issuer) {
         store_tile<false, false>(t, taddr, token_tile, t.ct * kTileM + quarter * 32 + lane, n_out, out);
       } else {
@@ -388,19 +405,20 @@ int stages_for(bool gate_up, int token_tile, int* smem_bytes, int reserve = 0) {
   return stages;
 }
 
-template <bool kGateUp, bool kGather = false>
+template <bool kGateUp, bool kGather = false, bool kPair = false>
 cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
   const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
-  const int n_ct = (n_out + kTileM - 1) / kTileM;
+  const int tile_channels = kPair ? 2 * kTileM : kTileM;
+  const int n_ct = (n_out + tile_channels - 1) / tile_channels;
   const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
   const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
-  const int smem = kGateUp ? p.gemm_smem_gate_up : p.gemm_smem_down;
-  const int stages = kGateUp ? p.gemm_stages_gate_up : p.gemm_stages_down;
+  const int smem = kGateUp ? p.gemm_smem_gate_up : kPair ? p.gemm_smem_down_pair : p.gemm_smem_down;
+  const int stages = kGateUp ? p.gemm_stages_gate_up : kPair ? p.gemm_stages_down_pair : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
-  launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
+  launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
@@ -419,8 +437,12 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
 
 int configure_tc(B200MoePlan& p) {
   p.gemm_stages_gate_up = stages_for(true, p.token_tile, &p.gemm_smem_gate_up);
-  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down,
-                                  p.buf.ep_row_dest ? 2 * static_cast<int>(kEpiBufBytes) : 0);
+  const int epi_reserve = p.buf.ep_row_dest ? 2 * static_cast<int>(kEpiBufBytes) : 0;
+  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down, epi_reserve);
+  p.gemm_stages_down_pair = stages_for(true, p.token_tile, &p.gemm_smem_down_pair, epi_reserve);   // two boxes per stage
+  // Pair tiles once an expert averages more than one token tile (shape-only): below that every weight tile is
+  // fetched once anyway and the finer 128-channel tiles balance the SMs better.
+  p.down_pair = p.token_tile == 128 && static_cast<long long>(p.routes) > static_cast<long long>(p.shape.experts) * 128;
   if (p.gemm_stages_gate_up < 2 || p.gemm_stages_down < 2) {
     set_error("token_tile %d leaves fewer than 2 shared-memory stages", p.token_tile);
     return B200MOE_ERR_INVALID;
@@ -434,6 +456,9 @@ int configure_tc(B200MoePlan& p) {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemLimit);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemLimit);
   if (e != cudaSuccess) {
     set_error("cudaFuncSetAttribute(shared memory) failed: %s", cudaGetErrorString(e));
     return B200MOE_ERR_CUDA;
@@ -445,7 +470,7 @@ cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained
   return p.gather ? launch_tc<true, true>(p, s, chained) : launch_tc<true>(p, s, chained);
 }
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
-  return launch_tc<false>(p, s, chained);
+  return p.down_pair ? launch_tc<false, false, true>(p, s, chained) : launch_tc<false>(p, s, chained);
 }
 
 }  // namespace b200moe

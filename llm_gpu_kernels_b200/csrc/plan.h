@@ -33,6 +33,8 @@ struct B200MoePlan {
   int router_smem = 0, router_stages = 0, router_ksplit = 1;  // ksplit = CTAs per cluster sharing one token tile
   int gemm_smem_gate_up = 0, gemm_stages_gate_up = 0;
   int gemm_smem_down = 0, gemm_stages_down = 0;
+  int gemm_smem_down_pair = 0, gemm_stages_down_pair = 0;   // down projection over 256-channel pair tiles
+  bool down_pair = false;
   // W4A16 kernels: packed-stage ring, operand-stage ring, dynamic shared memory
   int w4_packed_gate_up = 0, w4_operand_gate_up = 0, w4_smem_gate_up = 0;
   int w4_packed_down = 0, w4_operand_down = 0, w4_smem_down = 0;
