@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 /* error codes */
 #define B200MOE_OK 0
@@ -80,6 +80,13 @@ typedef struct {
                              the W4 weight-streaming kernel): the dispatch writes source_rows instead of copying rows
                              and the gate/up kernel gathers the token rows itself. B200MoeWorkspace.gathers reports
                              what the plan resolved; grouped_input may then be NULL and is left untouched. */
+  int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice (256-channel pair tiles once an expert
+                             averages more than one 128-row token tile), 1 = pair tiles, 2 = 128-channel tiles. The two
+                             differ in the FP32 summation order over K (one running sum per channel tile against an
+                             even-K and an odd-K partial sum), so results agree to rounding, not to the bit; two plans
+                             that must give identical bits (an expert-parallel layer and its single-GPU twin) pin the
+                             same value. B200MoeWorkspace.down_pair reports what the plan resolved. */
+  int32_t reserved[1];
 } B200MoeShape;
 
 /* Bytes of every workspace buffer the caller must allocate (256-byte aligned
@@ -104,6 +111,8 @@ typedef struct {
   int32_t schedule;     /* resolved schedule */
   int32_t launches;     /* kernels one forward enqueues */
   int32_t gathers;      /* 1: gate/up gathers token rows through source_rows; grouped_input is not written */
+  int32_t down_pair;    /* 1: the down projection runs over 256-channel pair tiles (see B200MoeShape.down_tiles) */
+  int32_t reserved;
 } B200MoeWorkspace;
 
 /* Device pointers. x, weights, ids, routing_weights belong to the caller;

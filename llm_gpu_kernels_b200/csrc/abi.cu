@@ -219,6 +219,15 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   }
   const int blocks = (p->partitions + kDispatchWarps - 1) / kDispatchWarps;
   p->chain_words = 1 + s.experts;
+  // Down projection over pair tiles once an expert averages more than one token tile (shape-only): below that every
+  // weight tile is fetched once anyway and the finer 128-channel tiles balance the SMs better.
+  if (s.down_tiles < 0 || s.down_tiles > 2) {
+    delete p;
+    set_error("down_tiles must be 0 (shape-only choice), 1 (pair tiles) or 2 (128-channel tiles)");
+    return B200MOE_ERR_INVALID;
+  }
+  p->down_pair = schedule == B200MOE_SCHEDULE_TCGEN05 && !is_w4(s.down_format) && !s.route_only && tile == 128 &&
+                 (s.down_tiles == 1 || (s.down_tiles == 0 && r > static_cast<long long>(s.experts) * 128));
   // gathering gate/up: the BF16 tensor-core kernel, or the W4 weight-streaming kernel (token tile 16)
   p->gather = s.fused_gather && schedule == B200MOE_SCHEDULE_TCGEN05 && !s.route_only && !s.external_dispatch &&
               r > 0 && (!is_w4(s.gate_up_format) || tile <= 16);
@@ -239,6 +248,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 2 + E) * 4);
   w.source_rows = p->gather ? R * 4 : 0;
   w.gathers = p->gather ? 1 : 0;
+  w.down_pair = p->down_pair ? 1 : 0;
   if (p->gather) w.grouped_input = 0;
   w.token_tile = tile;
   w.schedule = schedule;

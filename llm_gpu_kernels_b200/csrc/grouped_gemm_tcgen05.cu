@@ -440,9 +440,7 @@ int configure_tc(B200MoePlan& p) {
   const int epi_reserve = p.buf.ep_row_dest ? 2 * static_cast<int>(kEpiBufBytes) : 0;
   p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down, epi_reserve);
   p.gemm_stages_down_pair = stages_for(true, p.token_tile, &p.gemm_smem_down_pair, epi_reserve);   // two boxes per stage
-  // Pair tiles once an expert averages more than one token tile (shape-only): below that every weight tile is
-  // fetched once anyway and the finer 128-channel tiles balance the SMs better.
-  p.down_pair = p.token_tile == 128 && static_cast<long long>(p.routes) > static_cast<long long>(p.shape.experts) * 128;
+
   if (p.gemm_stages_gate_up < 2 || p.gemm_stages_down < 2) {
     set_error("token_tile %d leaves fewer than 2 shared-memory stages", p.token_tile);
     return B200MOE_ERR_INVALID;

@@ -39,9 +39,11 @@ def _run_rank(rank, world, port, shape, result):
         ref = O.moe_oracle(x[mine], gate_up, down, ids.cpu(), rw.cpu())
         m = O.error_metrics(out.float().cpu(), ref)
         assert m["relative_rms"] <= 5e-3 and m["normalized_max"] <= 8e-3, m
-        # parity 2: bit-identical to the single-GPU plan on the same tokens and routes
+        # parity 2: bit-identical to the single-GPU plan on the same tokens, routes and tile schedule
+        expert_plan = ep.backend.expert_plan
+        pinned = dict(token_tile=expert_plan.token_tile, down_pair=expert_plan.down_pair) if expert_plan.schedule == "tcgen05" else {}
         single = prepare_ranked_moe_launcher(x[mine].contiguous().to(dev), gate_up.to(dev), down.to(dev),
-                                             ids.clone(), rw.clone())
+                                             ids.clone(), rw.clone(), **pinned)
         assert torch.equal(single.run(), out)
         # parity 3: the counts of all ranks add up to the global histogram, bit-exact
         total = ep.backend.token_plan.counts.clone()
