@@ -79,7 +79,9 @@ typedef struct {
   int32_t fused_gather;   /* 1: do not materialise grouped_input when the kernels allow it (BF16 tensor-core gate/up, or
                              the W4 weight-streaming kernel): the dispatch writes source_rows instead of copying rows
                              and the gate/up kernel gathers the token rows itself. B200MoeWorkspace.gathers reports
-                             what the plan resolved; grouped_input may then be NULL and is left untouched. */
+                             what the plan resolved; grouped_input may then be NULL and is left untouched.
+                             1 stops gathering once experts average more than three 128-row tiles (routes > 384 x
+                             experts: the materialised copy is faster there), 2 gathers at any size. */
   int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice (256-channel pair tiles once an expert
                              averages more than one 128-row token tile), 1 = pair tiles, 2 = 128-channel tiles. The two
                              differ in the FP32 summation order over K (one running sum per channel tile against an

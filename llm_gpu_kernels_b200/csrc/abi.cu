@@ -228,9 +228,14 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   }
   p->down_pair = schedule == B200MOE_SCHEDULE_TCGEN05 && !is_w4(s.down_format) && !s.route_only && tile == 128 &&
                  (s.down_tiles == 1 || (s.down_tiles == 0 && r > static_cast<long long>(s.experts) * 128));
-  // gathering gate/up: the BF16 tensor-core kernel, or the W4 weight-streaming kernel (token tile 16)
+  // gathering gate/up: the BF16 tensor-core kernel, or the W4 weight-streaming kernel (token tile 16). Past about
+  // three 128-row tiles per expert the kernel is bound by operand latency out of L2, the cp.async gather answers later
+  // than a TMA box load and costs more than the row copy it saves (Qwen3 shape, forward with / without gather:
+  // 350 / 359 us at 2048 tokens, 506 / 511 at 4096, 898 / 891 at 8192), so fused_gather = 1 stops there;
+  // fused_gather = 2 gathers regardless.
   p->gather = s.fused_gather && schedule == B200MOE_SCHEDULE_TCGEN05 && !s.route_only && !s.external_dispatch &&
-              r > 0 && (!is_w4(s.gate_up_format) || tile <= 16);
+              r > 0 && (!is_w4(s.gate_up_format) || tile <= 16) &&
+              (s.fused_gather == 2 || r <= static_cast<long long>(s.experts) * 384);
 
   B200MoeWorkspace& w = p->ws;
   const size_t T = s.tokens, H = s.hidden, I = s.intermediate, E = s.experts, R = r;

@@ -142,7 +142,10 @@ __device__ __forceinline__ bool return_tile_rows(const Tile& t, uint32_t taddr, 
 // channel tile over all of K and there are no partial sums. Once an expert has several token tiles the kernels are
 // bound by what they pull out of L2 per FLOP (ncu at T=8192: 3.2 GB of operand tiles through L2 for the down
 // projection, 7.7 TB/s, tensor pipe 24 % busy); sharing the activation tile cuts that by a quarter.
-template <bool kGateUp, bool kGather = false, bool kPair = false>
+// kSingle (down projection at token tile 256) and kReturn (row_dest set) are template parameters as well: as run-time
+// switches they left the compiler one large epilogue with every variant in it, and the plain down kernel lost a
+// quarter of its speed to that.
+template <bool kGateUp, bool kGather = false, bool kPair = false, bool kSingle = false, bool kReturn = false>
 __global__ void __launch_bounds__(kGather ? kGatherThreads : kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_act,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ g_offsets,
@@ -152,7 +155,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                        const int* row_dest, const unsigned long long* ret_bases,
                        const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows) {
   static_assert(kGateUp || !kGather, "only the gate/up projection gathers token rows");
-  static_assert(!kGateUp || !kPair, "the pair tile is a schedule of the down projection");
+  static_assert(!kGateUp || !(kPair || kSingle || kReturn), "schedules of the down projection");
+  static_assert(!(kPair && kSingle), "the pair tile has two issuers");
   constexpr bool kTwoBoxes = kGateUp || kPair;          // two weight boxes per stage, one MMA issuer each
   constexpr int kTileChannels = kPair ? 2 * kTileM : kTileM;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -166,7 +170,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   // At token tile 256 an MMA (N = 256) takes longer than one thread needs to issue it, so the down projection runs
   // with ONE issuer and one partial sum: its accumulator is 256 columns and still double-buffered (the epilogue of
   // a K = I tile is too long to leave unoverlapped). gate/up needs gate + up = 512 columns either way.
-  const bool single_issuer = !kTwoBoxes && token_tile > 128;
+  constexpr bool single_issuer = kSingle;
   const int acc_cols = single_issuer ? token_tile : 2 * token_tile;   // gate and up, or the two partial sums of down
   const int num_acc = (2 * acc_cols <= 512) ? 2 : 1;
   uint32_t tmem_cols = 32;
@@ -188,8 +192,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     for (int q = 0; q < kItemRing; ++q) mbar_init(&c->item_ready[q], 1);
     mbar_init(&c->drain[0], 1);
     mbar_init(&c->drain[1], 1);
-    mbar_init(&c->epi_bar[0], 4);
-    mbar_init(&c->epi_bar[1], 4);
+    if (kReturn) {
+      mbar_init(&c->epi_bar[0], 4);
+      mbar_init(&c->epi_bar[1], 4);
+    }
     c->abort = 0;
     mbar_init_fence();
   }
@@ -356,7 +362,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (!__all_sync(0xffffffffu, mbar_wait(&c->tmem_full[acc], acc_phase, &c->abort, status))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * acc_cols) + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (!kGateUp && row_dest != nullptr) {
+      if (kReturn) {
         bool sent = return_tile_rows(t, taddr, token_tile, quarter, lane, n_out, row_dest, ret_bases, epi, c->epi_bar,
                                      epi_chunk, &c->abort, status, !single_issuer && !kPair, t.ct * kTileChannels);
         if (sent && kPair)
@@ -405,7 +411,7 @@ int stages_for(bool gate_up, int token_tile, int* smem_bytes, int reserve = 0) {
   return stages;
 }
 
-template <bool kGateUp, bool kGather = false, bool kPair = false>
+template <bool kGateUp, bool kGather = false, bool kPair = false, bool kSingle = false, bool kReturn = false>
 cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const auto& sh = p.shape;
   const int n_out = kGateUp ? sh.intermediate : sh.hidden;
@@ -418,7 +424,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const int stages = kGateUp ? p.gemm_stages_gate_up : kPair ? p.gemm_stages_down_pair : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
-  launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
+  launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair, kSingle, kReturn>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
@@ -446,20 +452,21 @@ int configure_tc(B200MoePlan& p) {
     return B200MOE_ERR_INVALID;
   }
   // the opt-in is per kernel, not per plan: always raise it to the device limit
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemLimit);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit);
-  if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(shared memory) failed: %s", cudaGetErrorString(e));
-    return B200MOE_ERR_CUDA;
+  const void* kernels[] = {
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<true, true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false, false, true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false, false, false, true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false, false, false, false, true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false, false, true, false, true>),
+      reinterpret_cast<const void*>(grouped_gemm_tc_kernel<false, false, false, true, true>)};
+  for (const void* kernel : kernels) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(shared memory) failed: %s", cudaGetErrorString(e));
+      return B200MOE_ERR_CUDA;
+    }
   }
   return B200MOE_OK;
 }
@@ -468,7 +475,14 @@ cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained
   return p.gather ? launch_tc<true, true>(p, s, chained) : launch_tc<true>(p, s, chained);
 }
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
-  return p.down_pair ? launch_tc<false, false, true>(p, s, chained) : launch_tc<false>(p, s, chained);
+  const bool single = !p.down_pair && p.token_tile > 128;   // one MMA issuer, one partial sum (see the kernel)
+  if (p.buf.ep_row_dest) {
+    if (p.down_pair) return launch_tc<false, false, true, false, true>(p, s, chained);
+    return single ? launch_tc<false, false, false, true, true>(p, s, chained)
+                  : launch_tc<false, false, false, false, true>(p, s, chained);
+  }
+  if (p.down_pair) return launch_tc<false, false, true>(p, s, chained);
+  return single ? launch_tc<false, false, false, true>(p, s, chained) : launch_tc<false>(p, s, chained);
 }
 
 }  // namespace b200moe

@@ -24,6 +24,7 @@ from . import _native, _ops
 from .gemm import GemmConfig
 
 STAGE_NAMES = ("router", "dispatch", "gate_up_swiglu", "down", "combine")
+_GATHER = {False: 1, True: 0, "never": 2}   # keep_grouped_input -> B200MoeShape.fused_gather
 _SCHEDULES = {None: _native.SCHEDULE_AUTO, "auto": _native.SCHEDULE_AUTO,
               "generic": _native.SCHEDULE_GENERIC, "tcgen05": _native.SCHEDULE_TCGEN05}
 
@@ -231,7 +232,11 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
     W4G128 int32 word tensor instead of a BF16 tensor. Unless ``keep_grouped_input`` is set, a plan whose
     gate/up kernel can gather token rows itself does not materialise ``grouped_input`` (it stays an empty
     tensor): the dispatch then writes ``source_rows`` (grouped row -> token) instead of copying rows.
+    ``keep_grouped_input``: False = the library decides by shape (it gathers until experts average more than three
+    128-row tiles), True = always materialise, "never" = gather whenever the kernels can.
     """
+    if keep_grouped_input not in _GATHER:
+        raise ValueError('keep_grouped_input must be False, True or "never"')
     e, h, intermediate = _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_scales,
                                    down_scales, route_only_experts)
     if valid_routes is not None and (valid_routes.dtype != torch.int32 or valid_routes.numel() != 1
@@ -253,7 +258,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           use_router=int(router_weight is not None),
                           route_only=0 if route_only_experts is None else (1 if copy_rows else 2),
                           router_bf16_weights=int(bool(router_bf16_weights)), unchained=int(bool(unchained)),
-                          fused_gather=int(not keep_grouped_input),
+                          fused_gather=_GATHER[keep_grouped_input],
                           down_tiles=0 if down_pair is None else (1 if down_pair else 2))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
@@ -320,7 +325,8 @@ def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, s
     ``residual`` ([T,H] bf16, read every forward) is added to the layer result inside the combine kernel:
     ``output = bf16(residual + bf16(layer))``, the model's residual add without a round trip through HBM.
     ``keep_grouped_input=True`` makes every forward fill the ``grouped_input`` workspace tensor as the reference's
-    dispatch does; by default the gate/up kernel reads the token rows through ``source_rows`` where it can.
+    dispatch does; by default the gate/up kernel reads the token rows through ``source_rows`` where that is
+    faster (until experts average more than three 128-row tiles); ``"never"`` gathers whenever the kernels can.
     ``down_pair`` pins the tile schedule of the BF16 down projection (None = shape-only choice); the two schedules
     sum over K in a different order, so plans that must agree to the bit pin the same one."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,

@@ -117,7 +117,7 @@ def test_qwen_skewed_routing_8192(dev, qwen, skew_case):
     _, gate_up, down = qwen["cpu"]
     _, gate_up_d, down_d = qwen["gpu"]
     x, ids, rw = skew_case
-    p = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev))
+    p = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev), keep_grouped_input="never")
     assert p.base.token_tile == 128 and p.base.gathers
     out = p.run()
     torch.cuda.synchronize()
@@ -133,6 +133,9 @@ def test_qwen_skewed_routing_8192(dev, qwen, skew_case):
     kept = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev), keep_grouped_input=True)
     assert not kept.base.gathers and torch.equal(kept.run(), out)
     check_dispatch(kept.base, x, ids, 128)
+    # at this size (512 rows per expert on average) the shape-only choice is the materialised dispatch
+    auto = prepare_ranked_moe_launcher(x.to(dev), gate_up_d, down_d, ids.to(dev), rw.to(dev))
+    assert not auto.base.gathers and torch.equal(auto.run(), out)
 
 
 def test_qwen_skewed_routing_8192_w4(dev, qwen, skew_case):
