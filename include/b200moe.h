@@ -82,8 +82,8 @@ typedef struct {
                              what the plan resolved; grouped_input may then be NULL and is left untouched.
                              1 stops gathering once experts average more than three 128-row tiles (routes > 384 x
                              experts: the materialised copy is faster there), 2 gathers at any size. */
-  int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice (256-channel pair tiles once an expert
-                             averages more than one 128-row token tile), 1 = pair tiles, 2 = 128-channel tiles. The two
+  int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice (256-channel pair tiles up to
+                             token tile 128, one 128-channel tile at 256), 1 = pair tiles, 2 = 128-channel tiles. The two
                              differ in the FP32 summation order over K (one running sum per channel tile against an
                              even-K and an odd-K partial sum), so results agree to rounding, not to the bit; two plans
                              that must give identical bits (an expert-parallel layer and its single-GPU twin) pin the

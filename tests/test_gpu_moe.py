@@ -115,6 +115,24 @@ def test_tcgen05_small_shapes(dev, t, e, k, h, i, pattern, tile, keep):
     assert m["relative_rms"] <= REL_RMS_BF16, m
 
 
+@pytest.mark.parametrize("t,e,k,h,i,pattern,tile", [c for c in TC if 0 < c[6] <= 128])
+def test_down_pair_tiles(dev, t, e, k, h, i, pattern, tile):
+    """The down projection over 256-channel pair tiles (one MMA issuer per 128 channels, no partial sums) at every
+    token tile it serves, including H that is not a multiple of 256 (the second weight box runs past the expert)."""
+    cpu = make_inputs(t, e, k, h, i, pattern=pattern, seed=100 + t, wscale=0.1, signed=True)
+    gpu = tuple(a.to(dev) for a in cpu)
+    p = prep()(*gpu, schedule="tcgen05", token_tile=tile, down_pair=True)
+    assert p.base.down_pair and p.base.token_tile == tile
+    out = p.run()
+    torch.cuda.synchronize()
+    p.check_inputs()
+    check_output(out, cpu)
+    split = prep()(*gpu, schedule="tcgen05", token_tile=tile, down_pair=False)
+    assert not split.base.down_pair
+    m = O.error_metrics(out.float().cpu(), split.run().float().cpu())
+    assert m["relative_rms"] <= REL_RMS_BF16, m
+
+
 @pytest.mark.parametrize("tokens", [17, 193, 1024])
 def test_qwen_shape_full_layer(dev, tokens):
     """BASELINE config 2: router + experts, Qwen3-30B-A3B layer shape, seeded synthetic weights."""
