@@ -58,6 +58,11 @@ constexpr int kGatherMaxIters = 16;                           // 16-byte chunks 
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
+// Head of the gate/up weights that the gate/up CTAs pull into L2 while router and dispatch still run (HBM is idle
+// then). Qwen3 shape, forward at 17 / 193 / 1024 tokens: 142.4 / 197.7 / 230.7 us without, 138.0 / 192.4 / 225.8 with
+// 32 MB, 137.5 / 190.8 / 223.8 with 64 MB, 135.9 / 189.6 / 226.0 with 96 MB (L2 holds 126 MB).
+constexpr long long kPrefetchBytes = 64ll << 20;
+constexpr uint32_t kPrefetchChunk = 8192;            // bytes per L2 prefetch instruction
 static_assert(kItemRing >= kMaxStages + 3, "producer could lap the item ring");
 // Staging of the epilogue that returns rows to other ranks: 16 rows x 128 channels BF16 (+16 bytes of padding per
 // row), two buffers.
@@ -153,7 +158,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                        int E, int n_out, int k_dim, int w_rows_per_expert, int token_tile, int num_stages,
                        int stream_weights, int* chain_done, int chain_need, int* tile_counter,
                        const int* row_dest, const unsigned long long* ret_bases,
-                       const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows) {
+                       const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows,
+                       const unsigned char* __restrict__ prefetch_base, int prefetch_chunks) {
   static_assert(kGateUp || !kGather, "only the gate/up projection gathers token rows");
   static_assert(!kGateUp || !(kPair || kSingle || kReturn), "schedules of the down projection");
   static_assert(!(kPair && kSingle), "the pair tile has two issuers");
@@ -201,6 +207,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   }
   if (warp == 1) {
     tmem_alloc(&c->tmem_base, tmem_cols);
+  }
+  // gate/up: the kernels before this one (router, dispatch) leave HBM idle, and this CTA is resident long before they
+  // finish. Pull the head of the weight tensor - what the grid will read first, whatever the routing turns out to
+  // be - into L2 meanwhile; the TMA loads below then hit there.
+  if (kGateUp && prefetch_chunks > 0) {
+    const int per_cta = (prefetch_chunks + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const int first = static_cast<int>(blockIdx.x) * per_cta;
+    const int last = first + per_cta < prefetch_chunks ? first + per_cta : prefetch_chunks;
+    for (int chunk = first + static_cast<int>(threadIdx.x); chunk < last; chunk += static_cast<int>(blockDim.x))
+      prefetch_l2_bulk(prefetch_base + static_cast<size_t>(chunk) * kPrefetchChunk, kPrefetchChunk);
   }
   // Everything above overlapped with the previous kernel. A chained down kernel does not wait for the
   // gate/up grid: it can only be scheduled after every gate/up CTA has passed its own wait (below), so
@@ -424,6 +440,8 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const int stages = kGateUp ? p.gemm_stages_gate_up : kPair ? p.gemm_stages_down_pair : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
+  const long long weight_bytes = static_cast<long long>(sh.experts) * 2 * sh.intermediate * sh.hidden * 2;
+  const int prefetch_chunks = static_cast<int>((weight_bytes < kPrefetchBytes ? weight_bytes : kPrefetchBytes) / kPrefetchChunk);
   launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair, kSingle, kReturn>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
@@ -435,7 +453,9 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
       chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr),
       kGateUp ? static_cast<const int*>(nullptr) : static_cast<const int*>(p.buf.ep_row_dest),
       static_cast<const unsigned long long*>(p.buf.ep_return_bases), static_cast<const __nv_bfloat16*>(p.buf.x),
-      static_cast<const int*>(p.buf.source_rows));
+      static_cast<const int*>(p.buf.source_rows),
+      kGateUp ? static_cast<const unsigned char*>(p.buf.gate_up) : static_cast<const unsigned char*>(nullptr),
+      kGateUp ? prefetch_chunks : 0);
   return cudaPeekAtLastError();
 }
 

@@ -68,6 +68,12 @@ __device__ __forceinline__ bool mbar_wait_plain(uint64_t* bar, uint32_t parity) 
   return true;
 }
 
+// Asynchronous prefetch of `bytes` (a multiple of 16, 16-byte aligned address) of global memory into L2.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* global_ptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(global_ptr)), "r"(bytes)
+               : "memory");
+}
+
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
