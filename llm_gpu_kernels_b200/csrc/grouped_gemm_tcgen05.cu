@@ -58,11 +58,6 @@ constexpr int kGatherMaxIters = 16;                           // 16-byte chunks 
 constexpr int kMaxStages = 12;
 constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;  // 16 KB
 constexpr int kCtrlBytes = 4096;
-// Head of the gate/up weights that the gate/up CTAs pull into L2 while router and dispatch still run (HBM is idle
-// then). Qwen3 shape, forward at 17 / 193 / 1024 tokens: 142.4 / 197.7 / 230.7 us without, 138.0 / 192.4 / 225.8 with
-// 32 MB, 137.5 / 190.8 / 223.8 with 64 MB, 135.9 / 189.6 / 226.0 with 96 MB (L2 holds 126 MB).
-constexpr long long kPrefetchBytes = 64ll << 20;
-constexpr uint32_t kPrefetchChunk = 8192;            // bytes per L2 prefetch instruction
 static_assert(kItemRing >= kMaxStages + 3, "producer could lap the item ring");
 // Staging of the epilogue that returns rows to other ranks: 16 rows x 128 channels BF16 (+16 bytes of padding per
 // row), two buffers.
@@ -211,13 +206,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   // gate/up: the kernels before this one (router, dispatch) leave HBM idle, and this CTA is resident long before they
   // finish. Pull the head of the weight tensor - what the grid will read first, whatever the routing turns out to
   // be - into L2 meanwhile; the TMA loads below then hit there.
-  if (kGateUp && prefetch_chunks > 0) {
-    const int per_cta = (prefetch_chunks + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-    const int first = static_cast<int>(blockIdx.x) * per_cta;
-    const int last = first + per_cta < prefetch_chunks ? first + per_cta : prefetch_chunks;
-    for (int chunk = first + static_cast<int>(threadIdx.x); chunk < last; chunk += static_cast<int>(blockDim.x))
-      prefetch_l2_bulk(prefetch_base + static_cast<size_t>(chunk) * kPrefetchChunk, kPrefetchChunk);
-  }
+  if (kGateUp) prefetch_head(prefetch_base, prefetch_chunks);
   // Everything above overlapped with the previous kernel. A chained down kernel does not wait for the
   // gate/up grid: it can only be scheduled after every gate/up CTA has passed its own wait (below), so
   // the dispatch metadata is complete, and it synchronises on activated rows through chain_done.
@@ -441,7 +430,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   // weights are streamed (evict-first) when an expert rarely has a second token tile
   const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
   const long long weight_bytes = static_cast<long long>(sh.experts) * 2 * sh.intermediate * sh.hidden * 2;
-  const int prefetch_chunks = static_cast<int>((weight_bytes < kPrefetchBytes ? weight_bytes : kPrefetchBytes) / kPrefetchChunk);
+  const int prefetch_chunks = prefetch_head_chunks(weight_bytes);
   launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair, kSingle, kReturn>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
       kGateUp ? p.tm_gate_up_w : p.tm_down_w, kGateUp ? p.tm_grouped : p.tm_activated,
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),

@@ -151,7 +151,8 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
                         const int* __restrict__ g_tasks, int* __restrict__ status, int E, int n_out, int k_dim,
                         int w_rows_per_expert, int token_tile, int num_stages, int stream_weights, int hi_offset,
                         int tile_channels, int* chain_done, int chain_need, int* tile_counter,
-                        const int* __restrict__ source_rows) {
+                        const int* __restrict__ source_rows, const unsigned char* __restrict__ prefetch_base,
+                        int prefetch_chunks) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   Ctrl* c = reinterpret_cast<Ctrl*>(smem_raw);
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -178,6 +179,7 @@ grouped_gemm_w4r_kernel(const __grid_constant__ CUtensorMap tm_words, const __nv
   }
   // A chained down kernel can only be scheduled once every gate/up CTA has passed its own wait (gate/up lets its
   // dependents go after it), so the dispatch metadata is complete; activated rows are awaited per expert below.
+  if (kGateUp) prefetch_head(prefetch_base, prefetch_chunks);   // packed words into L2 while router / dispatch run
   if (!chained) pdl_wait();
   if (kGateUp) pdl_launch_dependents();
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
@@ -439,7 +441,9 @@ cudaError_t launch_w4r(const B200MoePlan& p, cudaStream_t s, bool chained) {
       chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
       kGroupWarps * ((sh.intermediate + 127) / 128),  // storing warps x gate/up channel tiles per token tile
       chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr),
-      kGateUp && p.gather ? static_cast<const int*>(p.buf.source_rows) : static_cast<const int*>(nullptr));
+      kGateUp && p.gather ? static_cast<const int*>(p.buf.source_rows) : static_cast<const int*>(nullptr),
+      kGateUp ? static_cast<const unsigned char*>(p.buf.gate_up) : static_cast<const unsigned char*>(nullptr),
+      kGateUp ? prefetch_head_chunks(static_cast<long long>(sh.experts) * 2 * sh.intermediate * sh.hidden / 2) : 0);
   return cudaPeekAtLastError();
 }
 
