@@ -207,11 +207,14 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   p->routes = static_cast<int>(r);
   p->schedule = schedule;
   p->token_tile = tile;
-  p->dispatch_fused = r <= kFusedRoutes;
-  if (p->dispatch_fused) {  // 32 warps of one block share the routes
-    const int per_warp = round_up(static_cast<int>((r + 31) / 32), 32);
+  p->dispatch_fused = r <= static_cast<long long>(kFusedRoutes) * kFusedCluster;
+  if (p->dispatch_fused) {  // the 32 warps of each block of a cluster share the routes
+    p->dispatch_ctas = 1;   // 1, 2, 4 or 8
+    while (static_cast<long long>(p->dispatch_ctas) * kFusedRoutes < r) p->dispatch_ctas *= 2;
+    const int warps = 32 * p->dispatch_ctas;
+    const int per_warp = round_up(static_cast<int>((r + warps - 1) / warps), 32);
     p->warp_routes = per_warp < 32 ? 32 : per_warp;
-    p->partitions = 32;
+    p->partitions = warps;
   } else {
     const int per_warp = round_up(static_cast<int>((r + 511) / 512), 32);
     p->warp_routes = per_warp < 128 ? 128 : per_warp;

@@ -11,7 +11,9 @@
 //
 // Up to kFusedRoutes (2048) routes one 1024-thread block does count + scan + final
 // ranks / mapping in a single launch (warp histograms stay in shared memory)
-// and a second kernel copies the rows. Above that, three kernels:
+// and a second kernel copies the rows; up to 8 x 2048 routes a thread-block cluster of
+// 2, 4 or 8 such blocks does the same, exchanging per-expert totals through distributed
+// shared memory. Above that, three kernels:
 //  count   - every warp owns `warp_routes` consecutive routes and walks them 32
 //            at a time in order: __match_any_sync gives the lanes with the same
 //            expert, so rank-in-partition = running warp histogram + number of
@@ -154,7 +156,24 @@ dispatch_scan_kernel(int* __restrict__ hist, const int* __restrict__ flags, int*
   }
 }
 
-// One block does the whole dispatch metadata for up to kFusedRoutes routes.
+// Distributed shared memory: the word at the address of `local` in CTA `cta` of this cluster.
+__device__ __forceinline__ int ld_cluster(const int* local, unsigned cta) {
+  unsigned remote;
+  int v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"(static_cast<unsigned>(__cvta_generic_to_shared(local))), "r"(cta));
+  asm volatile("ld.shared::cluster.b32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// One kernel does the whole dispatch metadata: a block ranks up to kFusedRoutes routes, and a thread-block cluster of
+// 1, 2, 4 or 8 such blocks shares a larger forward - block c owns routes [c, c+1) x 32 x warp_routes, keeps its
+// per-warp histograms in its own shared memory and reads the other blocks' per-expert totals through distributed
+// shared memory, so the stable rank of a route is rank in its warp + rows of earlier warps of its block + rows of
+// earlier blocks. Every block computes the expert offsets; block 0 writes the metadata.
 template <typename IdT>
 __global__ void __launch_bounds__(1024)
 dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw, int* __restrict__ ranks,
@@ -164,8 +183,13 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
                       int warp_routes, int token_tile, int chain_words, int* __restrict__ source_rows, int K) {
   pdl_launch_dependents();
   pdl_wait();  // ids / routing weights may come from the router kernel just before
+  unsigned cta, ctas;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ctas));
   const int r_eff = valid_routes ? min(R, max(*valid_routes, 0)) : R;  // routes past r_eff are padding
   __shared__ int warp_hist[32][kMaxExperts];
+  __shared__ int s_total[kMaxExperts];   // rows of each expert among this block's routes (read by the other blocks)
+  __shared__ int s_base[kMaxExperts];    // rows of each expert in the blocks before this one
   __shared__ int s_off[kMaxExperts];
   __shared__ int s_scan[16];
   __shared__ int s_flags;
@@ -173,7 +197,9 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
   if (threadIdx.x == 0) s_flags = 0;
   for (int e = lane; e < E; e += 32) warp_hist[warp][e] = 0;
   __syncthreads();
-  const int begin = min(R, warp * warp_routes), end = min(R, begin + warp_routes);
+  const int part = static_cast<int>(cta) * 32 + warp;
+  const int begin = static_cast<int>(min(static_cast<long long>(R), static_cast<long long>(part) * warp_routes));
+  const int end = min(R, begin + warp_routes);
   const int iters = (end - begin + 31) >> 5;   // <= kFusedIters: kFusedRoutes / 32 warps / 32 lanes
   int my_flags = 0;
   int key[kFusedIters], rk[kFusedIters];
@@ -209,25 +235,45 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
 #pragma unroll 8
     for (int w = 0; w < 32; ++w) {
       const int c = warp_hist[w][e];
-      warp_hist[w][e] = total;  // base rank of warp w's partition inside expert e
+      warp_hist[w][e] = total;  // base rank of warp w's partition inside expert e, within this block
       total += c;
     }
+    s_total[e] = total;
+  }
+  int base = 0, flags = s_flags;
+  if (ctas > 1) {
+    cluster_sync();   // every block's s_total / s_flags is written
+    if (e < E) {
+      total = 0;
+      for (unsigned c = 0; c < ctas; ++c) {
+        const int v = ld_cluster(&s_total[e], c);
+        if (c < cta) base += v;
+        total += v;
+      }
+    }
+    if (e == 0)
+      for (unsigned c = 0; c < ctas; ++c) flags |= ld_cluster(&s_flags, c);
   }
   const int tiles = e < E ? (total + token_tile - 1) / token_tile : 0;
   int off, toff, ttotal;
   expert_prefix(e < E ? total : 0, tiles, s_scan, &off, &toff, &ttotal);
   if (e < E) {
-    counts[e] = total;
-    offsets[e] = off;
-    cursors[e] = 0;
-    tasks[e] = toff;
     s_off[e] = off;
-    if (e == E - 1) tasks[E] = ttotal;
+    s_base[e] = base;
   }
-  for (int i = e; i < chain_words; i += blockDim.x) router_flag[1 + i] = 0;  // see the scan kernel
-  if (e == 0) {
-    *status = s_flags | *router_flag;
-    *router_flag = 0;
+  if (cta == 0) {
+    if (e < E) {
+      counts[e] = total;
+      offsets[e] = off;
+      cursors[e] = 0;
+      tasks[e] = toff;
+      if (e == E - 1) tasks[E] = ttotal;
+    }
+    for (int i = e; i < chain_words; i += blockDim.x) router_flag[1 + i] = 0;  // see the scan kernel
+    if (e == 0) {
+      *status = flags | *router_flag;
+      *router_flag = 0;
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -236,7 +282,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
     if (it < iters && q < end) {
       int rank = -1, pos = -1;
       if (key[it] < E) {
-        rank = rk[it] + warp_hist[warp][key[it]];  // + base rank of this warp's partition in the expert
+        rank = rk[it] + warp_hist[warp][key[it]] + s_base[key[it]];  // + rows of earlier warps and earlier blocks
         pos = s_off[key[it]] + rank;
       }
       ranks[q] = rank;
@@ -244,6 +290,7 @@ dispatch_fused_kernel(const IdT* __restrict__ ids, const float* __restrict__ rw,
       if (source_rows != nullptr && pos >= 0) source_rows[pos] = q / K;
     }
   }
+  if (ctas > 1) cluster_sync();   // no block leaves while another may still read its shared memory
 }
 
 // Row copy for the fused path: grouped_input[mapping[q], :] = x[q / K, :], one warp per route.
@@ -351,11 +398,11 @@ cudaError_t launch_dispatch(const B200MoePlan& p, cudaStream_t s) {
     auto* mapping = static_cast<int*>(p.buf.mapping);
     int* source_rows = p.gather ? static_cast<int*>(p.buf.source_rows) : nullptr;
     if (sh.ids_are_int64) {
-      launch_pdl(dispatch_fused_kernel<long long>, dim3(1), dim3(1024), 0, s, static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
+      launch_pdl_cluster(dispatch_fused_kernel<long long>, p.dispatch_ctas, dim3(1024), 0, s, static_cast<const long long*>(p.buf.ids), rw, ranks, mapping,
                                                           counts, offsets, cursors, tasks, status, router_flag, valid, R,
                                                           E, p.warp_routes, p.token_tile, p.chain_words, source_rows, sh.topk);
     } else {
-      launch_pdl(dispatch_fused_kernel<int>, dim3(1), dim3(1024), 0, s, static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
+      launch_pdl_cluster(dispatch_fused_kernel<int>, p.dispatch_ctas, dim3(1024), 0, s, static_cast<const int*>(p.buf.ids), rw, ranks, mapping, counts,
                                                     offsets, cursors, tasks, status, router_flag, valid, R, E,
                                                     p.warp_routes, p.token_tile, p.chain_words, source_rows, sh.topk);
     }

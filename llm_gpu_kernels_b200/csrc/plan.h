@@ -18,7 +18,8 @@ struct B200MoePlan {
   // dispatch partition: each warp ranks `warp_routes` consecutive routes
   int warp_routes = 0;
   int partitions = 0;      // number of warp partitions = ceil(R / warp_routes)
-  bool dispatch_fused = false;  // one-block count + scan + mapping (R <= kFusedRoutes)
+  bool dispatch_fused = false;  // count + scan + mapping in one kernel (R <= kFusedRoutes per CTA of a cluster)
+  int dispatch_ctas = 1;        // CTAs of that kernel's thread-block cluster
   bool gather = false;          // gate/up reads token rows through source_rows; the dispatch copies no rows
   int chain_words = 0;     // scratch words after the router flag that the dispatch zeroes: tile counter + done[E]
   // TMA descriptors (tcgen05 schedule)
@@ -88,8 +89,10 @@ inline size_t router_flag_index(const B200MoePlan& p) {
 }
 
 constexpr int kGenericTile = 32;   // rows per tile of the CUDA-core schedule
-constexpr int kFusedRoutes = 2048;   // up to here one 1024-thread block builds the dispatch metadata; above, the
-                                     // ranking (a serial __match_any_sync walk per warp) is spread over many SMs
+constexpr int kFusedRoutes = 2048;   // one 1024-thread block ranks up to this many routes; a cluster of up to
+constexpr int kFusedCluster = 8;     // kFusedCluster such blocks builds the dispatch metadata in one kernel (the
+                                     // histograms meet through distributed shared memory); above, the ranking
+                                     // is spread over many SMs by three kernels
 constexpr int kDispatchWarps = 8;  // warps per block of the count / permute kernels
 
 }  // namespace b200moe

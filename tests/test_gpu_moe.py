@@ -202,6 +202,28 @@ def test_large_route_count_multi_block_dispatch(dev, pattern):
     check_output(out, cpu)
 
 
+@pytest.mark.parametrize("tokens,dt", [(300, torch.int32), (1000, torch.int64), (2040, torch.int32), (2048, torch.int32)])
+@pytest.mark.parametrize("pattern", ["random", "hot", "all_hot"])
+def test_cluster_dispatch(dev, tokens, dt, pattern):
+    """2049..16384 routes: the one-kernel dispatch as a thread-block cluster of 2 / 4 / 8 blocks that exchange their
+    per-expert totals through distributed shared memory. Same stable order, bit-exact; a bad id and a non-finite
+    weight in the LAST block's routes reach the status word that block 0 writes."""
+    cpu = make_inputs(tokens, 64, 8, 64, 64, pattern=pattern, seed=78, wscale=0.2, signed=True, id_dtype=dt)
+    gpu = tuple(a.to(dev) for a in cpu)
+    p = prep()(*gpu)
+    out = p.run()
+    torch.cuda.synchronize()
+    p.check_inputs()
+    check_dispatch(p.base, cpu[0], cpu[3], 64)
+    check_output(out, cpu)
+    ids, rw = gpu[3], gpu[4]
+    ids[tokens - 1, 7] = 64
+    rw[tokens - 2, 3] = float("inf")
+    p.run()
+    assert int(p.base.status.item()) == 3
+    assert int(p.base.mapping[-1]) == -1 and int(p.base.ranks[-1]) == -1
+
+
 @pytest.mark.parametrize("schedule", [None, "generic"])
 def test_router_bf16_rounded_weights(dev, schedule):
     """The captured model's convention: weights rounded through BF16, then promoted (capture script :587-588)."""
