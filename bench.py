@@ -750,7 +750,7 @@ def main_ep(args, dev, peaks, rank, world):
             alt = ep_case(f"headline_{other}", QWEN, args.tokens, x_rank, local, wr, None, dev, timer, rank, world,
                           other, peaks, full_weights=full, oracle_rows=0, warmup=args.warmup)
             configs[f"headline_{other}"] = {kk: alt[kk] for kk in ("ms", "tokens_per_s", "timing", "parity")}
-            # BASELINE config 4: T=8192 over all ranks, Zipf(1.2) popularity prior, fixed routes from the host
+            # benchmark configuration 4: T=8192 over all ranks, Zipf(1.2) popularity prior, fixed routes from the host
             t_all = 8192
             gz = torch.Generator().manual_seed(4)
             x_all = torch.randn(t_all, h, generator=gz).bfloat16()
@@ -765,7 +765,7 @@ def main_ep(args, dev, peaks, rank, world):
         del full, local
         torch.cuda.empty_cache()
         if MIXTRAL["experts"] % world == 0 and not args.only_headline:
-            # BASELINE config 5: Mixtral-8x7B layer shape, T=32768 over all ranks, 8/N experts per GPU (one expert per
+            # benchmark configuration 5: Mixtral-8x7B layer shape, T=32768 over all ranks, 8/N experts per GPU (one expert per
             # GPU at N=8). Every rank draws only its own experts' weights, each from a seed of its own; rank 0
             # redraws the experts its sampled tokens use for the oracle check.
             m = MIXTRAL

@@ -83,7 +83,7 @@ def test_odd_shapes_generic(dev, t, e, k, h, i, dt, pattern, signed):
 
 # --- tensor-core schedule: small aligned shapes incl. ragged K tails and many token tiles
 TC = [
-    (64, 8, 2, 256, 128, "random", 0),       # BASELINE tiny shape, fixed routes
+    (64, 8, 2, 256, 128, "random", 0),       # the tiny benchmark shape, fixed routes
     (17, 16, 4, 128, 64, "random", 16),
     (33, 4, 2, 192, 96, "duplicate", 16),    # K tails: 192 = 3x64, 96 = 64 + 32
     (40, 8, 8, 72, 200, "random", 32),       # H, I not multiples of 64 / 128
@@ -135,7 +135,7 @@ def test_down_pair_tiles(dev, t, e, k, h, i, pattern, tile):
 
 @pytest.mark.parametrize("tokens", [17, 193, 1024])
 def test_qwen_shape_full_layer(dev, tokens):
-    """BASELINE config 2: router + experts, Qwen3-30B-A3B layer shape, seeded synthetic weights."""
+    """benchmark configuration 2: router + experts, Qwen3-30B-A3B layer shape, seeded synthetic weights."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
     wr, gate_up, down, x = seeded_layer(0, tokens, 2048, 768, 128)
     ids = torch.zeros(tokens, 8, dtype=torch.int32, device=dev)
@@ -261,7 +261,7 @@ def test_residual_added_in_combine(dev, schedule, h):
 
 
 def test_tiny_layer_golden(dev, golden_dir):
-    """BASELINE config 1 against the reference's own output on the same seeded inputs."""
+    """benchmark configuration 1 against the reference's own output on the same seeded inputs."""
     from llm_gpu_kernels_b200.moe_ranked import prepare_ranked_moe_launcher
     g = torch.load(golden_dir / "tiny_layer_seed0.pt")
     wr, gate_up, down, x = seeded_layer(0, 64, 256, 128, 8)

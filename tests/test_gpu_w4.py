@@ -92,7 +92,7 @@ def qwen_w4():
 
 @pytest.mark.parametrize("tokens", [17, 193, 1024])
 def test_qwen_shape_w4(dev, qwen_w4, tokens):
-    """BASELINE config 3: Qwen3-30B-A3B layer shape, gate/up and down both W4G128, router on."""
+    """benchmark configuration 3: Qwen3-30B-A3B layer shape, gate/up and down both W4G128, router on."""
     from llm_gpu_kernels_b200.moe_w4_cuda import prepare_w4_moe
     wr, pg, pd, gate_up_deq, down_deq, _ = qwen_w4
     x = torch.randn(tokens, 2048, generator=torch.Generator().manual_seed(tokens)).bfloat16()
