@@ -588,7 +588,7 @@ def ep_case(name, shape, tokens, x_host, local_weights, wr, routes, dev, timer, 
     if full_weights is not None:
         # the single-GPU twin on the same tile schedule (the two down schedules sum over K in a different order)
         single = prepare_ranked_moe_launcher(x.clone(), full_weights[0], full_weights[1], ids.clone(), rw.clone(),
-                                             token_tile=expert_plan.token_tile, down_pair=expert_plan.down_pair)
+                                             token_tile=expert_plan.token_tile, down_tiles=expert_plan.down_tiles)
         ok_single = torch.equal(single.run(), out)
         torch.cuda.synchronize(dev)
         del single

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 3
+#define B200MOE_ABI_VERSION 4
 
 /* error codes */
 #define B200MOE_OK 0
@@ -82,12 +82,15 @@ typedef struct {
                              what the plan resolved; grouped_input may then be NULL and is left untouched.
                              1 stops gathering once experts average more than three 128-row tiles (routes > 384 x
                              experts: the materialised copy is faster there), 2 gathers at any size. */
-  int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice (256-channel pair tiles up to
-                             token tile 128, one 128-channel tile at 256), 1 = pair tiles, 2 = 128-channel tiles. The two
-                             differ in the FP32 summation order over K (one running sum per channel tile against an
-                             even-K and an odd-K partial sum), so results agree to rounding, not to the bit; two plans
-                             that must give identical bits (an expert-parallel layer and its single-GPU twin) pin the
-                             same value. B200MoeWorkspace.down_pair reports what the plan resolved. */
+  int32_t down_tiles;     /* BF16 tensor-core down projection: 0 = shape-only choice, 1 = pair tiles (256 output channels x
+                             token tile, token tile <= 128), 2 = 128-channel tiles with an even-K and an odd-K partial
+                             sum, 3 = wide tiles (128 channels x 256 rows: the down kernel re-tiles the experts at 256
+                             rows while gate/up keeps token tile 128; needs token tile 128; faster as a stage, no
+                             faster inside a forward, so never the choice at 0). The choice at 0: pair up to token
+                             tile 128, one 128-channel tile at token tile 256. 1 and 3 keep one running FP32 sum over K, 2 adds
+                             two partial sums, so its low-order bits differ; two plans that must give identical bits
+                             (an expert-parallel layer and its single-GPU twin) pin the same value.
+                             B200MoeWorkspace.down_tiles reports what the plan resolved. */
   int32_t reserved[1];
 } B200MoeShape;
 
@@ -113,7 +116,7 @@ typedef struct {
   int32_t schedule;     /* resolved schedule */
   int32_t launches;     /* kernels one forward enqueues */
   int32_t gathers;      /* 1: gate/up gathers token rows through source_rows; grouped_input is not written */
-  int32_t down_pair;    /* 1: the down projection runs over 256-channel pair tiles (see B200MoeShape.down_tiles) */
+  int32_t down_tiles;   /* the resolved B200MoeShape.down_tiles (1, 2 or 3); 0 where that option does not apply */
   int32_t reserved;
 } B200MoeWorkspace;
 

@@ -10,7 +10,7 @@ import threading
 from pathlib import Path
 
 LIBRARY_PATH = Path(__file__).resolve().parent / "libb200moe.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 STATUS_BAD_ID = 1
 STATUS_BAD_WEIGHT = 2
@@ -42,7 +42,7 @@ WORKSPACE_BUFFERS = ("output", "counts", "offsets", "cursors", "tasks", "mapping
 class Workspace(ctypes.Structure):
     _fields_ = [(name, ctypes.c_size_t) for name in WORKSPACE_BUFFERS + ("source_rows",)] + [
         ("token_tile", ctypes.c_int32), ("schedule", ctypes.c_int32), ("launches", ctypes.c_int32),
-        ("gathers", ctypes.c_int32), ("down_pair", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+        ("gathers", ctypes.c_int32), ("down_tiles", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 INPUT_BUFFERS = ("x", "router_weight", "gate_up", "gate_up_scales", "down", "down_scales", "ids",

@@ -224,16 +224,35 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   p->chain_words = 1 + s.experts;
   // Down projection over pair tiles once an expert averages more than one token tile (shape-only): below that every
   // weight tile is fetched once anyway and the finer 128-channel tiles balance the SMs better.
-  if (s.down_tiles < 0 || s.down_tiles > 2) {
+  if (s.down_tiles < 0 || s.down_tiles > 3) {
     delete p;
-    set_error("down_tiles must be 0 (shape-only choice), 1 (pair tiles) or 2 (128-channel tiles)");
+    set_error("down_tiles must be 0 (shape-only choice), 1 (pair tiles), 2 (128-channel tiles) or 3 (wide tiles)");
     return B200MOE_ERR_INVALID;
   }
-  // pair tiles by default wherever two accumulator sets of two tiles fit (token tile <= 128): fewer, longer tiles and no
-  // partial sums; forward 143.0 / 197.7 / 232.9 / 341.8 us against 145.0 / 200.0 / 240.2 / 353.9 us with 128-channel
-  // tiles at 17 / 193 / 1024 / 2048 tokens of the Qwen3 shape
-  p->down_pair = schedule == B200MOE_SCHEDULE_TCGEN05 && !is_w4(s.down_format) && !s.route_only && tile <= 128 &&
-                 s.down_tiles != 2;
+  // BF16 tensor-core down projection. Pair tiles wherever two accumulator sets of two tiles fit (token tile <= 128):
+  // fewer, longer tiles and no partial sums; forward 143.0 / 197.7 / 232.9 us against 145.0 / 200.0 / 240.2 us with
+  // 128-channel tiles at 17 / 193 / 1024 tokens of the Qwen3 shape. Wide tiles (the down kernel re-tiles at 256 rows,
+  // one issuer, two 256-column accumulators, while gate/up keeps token tile 128) are an explicit option only: alone
+  // the down stage gains (106.8 / 172.7 / 257.2 us against 116.0 / 182.5 / 308.4 us with pair tiles at 2048 / 4096 /
+  // 8192 tokens, half the passes over an expert's weights), inside a forward it does not (334.2 / 504.7 / 870.9 us
+  // against 330.3 / 508.0 / 871.7 us): there the activated rows are still in L2 and sharing them between two
+  // channel tiles, which is what pair tiles do, is worth as much.
+  p->down_tile = tile;
+  if (schedule == B200MOE_SCHEDULE_TCGEN05 && !is_w4(s.down_format) && !s.route_only) {
+    if (s.down_tiles == 3 && tile != 128) {
+      delete p;
+      set_error("down_tiles = 3 (wide tiles) needs token tile 128 (resolved token tile: %d)", tile);
+      return B200MOE_ERR_INVALID;
+    }
+    if (s.down_tiles == 3)
+      p->down_tiles = 3;
+    else if (tile <= 128 && s.down_tiles != 2)
+      p->down_tiles = 1;
+    else
+      p->down_tiles = 2;
+    if (p->down_tiles == 3) p->down_tile = 256;
+  }
+  p->down_pair = p->down_tiles == 1;
   // gathering gate/up: the BF16 tensor-core kernel, or the W4 weight-streaming kernel (token tile 16). Past about
   // three 128-row tiles per expert the kernel is bound by operand latency out of L2, the cp.async gather answers later
   // than a TMA box load and costs more than the row copy it saves (Qwen3 shape, forward with / without gather:
@@ -259,7 +278,7 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   w.scratch = align256((static_cast<size_t>(p->partitions) * E + blocks + 2 + E) * 4);
   w.source_rows = p->gather ? R * 4 : 0;
   w.gathers = p->gather ? 1 : 0;
-  w.down_pair = p->down_pair ? 1 : 0;
+  w.down_tiles = p->down_tiles;
   if (p->gather) w.grouped_input = 0;
   w.token_tile = tile;
   w.schedule = schedule;
@@ -399,7 +418,7 @@ int b200moe_plan_bind(B200MoePlan* p, const B200MoeBuffers* b) {
       return rc;
     }
     if (!p->gather && (rc = encode_2d(&p->tm_grouped, b->grouped_input, R, H, p->token_tile, false))) return rc;
-    if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->token_tile, false))) return rc;
+    if ((rc = encode_2d(&p->tm_activated, b->activated, R, I, p->down_tile, false))) return rc;
     if ((rc = configure_tc(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && (rc = configure_w4(*p))) return rc;
     if ((is_w4(s.gate_up_format) || is_w4(s.down_format)) && p->token_tile <= 64 && (rc = configure_w4t(*p))) return rc;

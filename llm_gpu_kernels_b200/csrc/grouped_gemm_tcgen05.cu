@@ -154,7 +154,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
                        int stream_weights, int* chain_done, int chain_need, int* tile_counter,
                        const int* row_dest, const unsigned long long* ret_bases,
                        const __nv_bfloat16* __restrict__ x, const int* __restrict__ source_rows,
-                       const unsigned char* __restrict__ prefetch_base, int prefetch_chunks) {
+                       const unsigned char* __restrict__ prefetch_base, int prefetch_chunks, int chain_tile) {
   static_assert(kGateUp || !kGather, "only the gate/up projection gathers token rows");
   static_assert(!kGateUp || !(kPair || kSingle || kReturn), "schedules of the down projection");
   static_assert(!(kPair && kSingle), "the pair tile has two issuers");
@@ -214,6 +214,27 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   // gate/up lets its dependents go only now, so that a chained down kernel inherits "dispatch complete"
   if (kGateUp) pdl_launch_dependents();
   load_tables(&c->tables, g_tasks, g_offsets, g_counts, E);
+  if (!kGateUp && chain_tile != token_tile) {
+    // wide tiles: `tasks` was built by the dispatch for gate/up's token tile; this kernel tiles the same experts at
+    // its own token_tile, so it rebuilds the prefix from the counts (one warp, E <= 256)
+    __syncthreads();
+    if (warp == 0) {
+      int run = 0;
+      for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int tiles = e < E ? (c->tables.counts[e] + token_tile - 1) / token_tile : 0;
+        int incl = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        if (e < E) c->tables.tasks[e] = run + incl - tiles;
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) c->tables.tasks[E] = run;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -240,7 +261,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         const Tile t = decode_tile(&c->tables, item, E, n_ct, token_tile);
         const int w_row = t.expert * w_rows_per_expert + t.ct * kTileChannels;
         if (chained && t.expert != ready_expert) {
-          const int need = chain_need * (c->tables.tasks[t.expert + 1] - c->tables.tasks[t.expert]);
+          // arrivals per gate/up token tile x gate/up token tiles of the expert (gate/up tiles at chain_tile rows)
+          const int need = chain_need * ((c->tables.counts[t.expert] + chain_tile - 1) / chain_tile);
           if (!wait_expert_done(chain_done + t.expert, need, &c->abort, status)) { ok = false; break; }
           ready_expert = t.expert;
         }
@@ -423,12 +445,13 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
   const int k_dim = kGateUp ? sh.hidden : sh.intermediate;
   const int tile_channels = kPair ? 2 * kTileM : kTileM;
   const int n_ct = (n_out + tile_channels - 1) / tile_channels;
-  const long long bound = (static_cast<long long>((p.routes + p.token_tile - 1) / p.token_tile) + sh.experts - 1) * n_ct;
+  const int token_tile = kGateUp ? p.token_tile : p.down_tile;
+  const long long bound = (static_cast<long long>((p.routes + token_tile - 1) / token_tile) + sh.experts - 1) * n_ct;
   const int grid = static_cast<int>(bound < p.num_sms ? bound : p.num_sms);
   const int smem = kGateUp ? p.gemm_smem_gate_up : kPair ? p.gemm_smem_down_pair : p.gemm_smem_down;
   const int stages = kGateUp ? p.gemm_stages_gate_up : kPair ? p.gemm_stages_down_pair : p.gemm_stages_down;
   // weights are streamed (evict-first) when an expert rarely has a second token tile
-  const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * p.token_tile;
+  const int stream_weights = static_cast<long long>(p.routes) <= static_cast<long long>(sh.experts) * token_tile;
   const long long weight_bytes = static_cast<long long>(sh.experts) * 2 * sh.intermediate * sh.hidden * 2;
   const int prefetch_chunks = prefetch_head_chunks(weight_bytes);
   launch_pdl(grouped_gemm_tc_kernel<kGateUp, kGather, kPair, kSingle, kReturn>, dim3(grid), dim3(kGather ? kGatherThreads : kThreads), smem, s,
@@ -436,7 +459,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
       static_cast<__nv_bfloat16*>(kGateUp ? p.buf.activated : p.buf.down_output),
       static_cast<const int*>(p.buf.offsets), static_cast<const int*>(p.buf.counts),
       static_cast<const int*>(p.buf.tasks), static_cast<int*>(p.buf.status), sh.experts, n_out, k_dim,
-      kGateUp ? 2 * sh.intermediate : sh.hidden, p.token_tile, stages, stream_weights,
+      kGateUp ? 2 * sh.intermediate : sh.hidden, token_tile, stages, stream_weights,
       chained ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 2 : static_cast<int*>(nullptr),
       4 * ((sh.intermediate + kTileM - 1) / kTileM),  // epilogue warps x gate/up channel tiles per token tile
       chained && !kGateUp ? static_cast<int*>(p.buf.scratch) + router_flag_index(p) + 1 : static_cast<int*>(nullptr),
@@ -444,7 +467,7 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
       static_cast<const unsigned long long*>(p.buf.ep_return_bases), static_cast<const __nv_bfloat16*>(p.buf.x),
       static_cast<const int*>(p.buf.source_rows),
       kGateUp ? static_cast<const unsigned char*>(p.buf.gate_up) : static_cast<const unsigned char*>(nullptr),
-      kGateUp ? prefetch_chunks : 0);
+      kGateUp ? prefetch_chunks : 0, p.token_tile);
   return cudaPeekAtLastError();
 }
 
@@ -453,8 +476,8 @@ cudaError_t launch_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
 int configure_tc(B200MoePlan& p) {
   p.gemm_stages_gate_up = stages_for(true, p.token_tile, &p.gemm_smem_gate_up);
   const int epi_reserve = p.buf.ep_row_dest ? 2 * static_cast<int>(kEpiBufBytes) : 0;
-  p.gemm_stages_down = stages_for(false, p.token_tile, &p.gemm_smem_down, epi_reserve);
-  p.gemm_stages_down_pair = stages_for(true, p.token_tile, &p.gemm_smem_down_pair, epi_reserve);   // two boxes per stage
+  p.gemm_stages_down = stages_for(false, p.down_tile, &p.gemm_smem_down, epi_reserve);
+  p.gemm_stages_down_pair = stages_for(true, p.down_tile, &p.gemm_smem_down_pair, epi_reserve);   // two boxes per stage
 
   if (p.gemm_stages_gate_up < 2 || p.gemm_stages_down < 2) {
     set_error("token_tile %d leaves fewer than 2 shared-memory stages", p.token_tile);
@@ -484,7 +507,7 @@ cudaError_t launch_gate_up_tc(const B200MoePlan& p, cudaStream_t s, bool chained
   return p.gather ? launch_tc<true, true>(p, s, chained) : launch_tc<true>(p, s, chained);
 }
 cudaError_t launch_down_tc(const B200MoePlan& p, cudaStream_t s, bool chained) {
-  const bool single = !p.down_pair && p.token_tile > 128;   // one MMA issuer, one partial sum (see the kernel)
+  const bool single = !p.down_pair && p.down_tile > 128;   // one MMA issuer, one partial sum (see the kernel)
   if (p.buf.ep_row_dest) {
     if (p.down_pair) return launch_tc<false, false, true, false, true>(p, s, chained);
     return single ? launch_tc<false, false, false, true, true>(p, s, chained)

@@ -36,6 +36,8 @@ struct B200MoePlan {
   int gemm_smem_down = 0, gemm_stages_down = 0;
   int gemm_smem_down_pair = 0, gemm_stages_down_pair = 0;   // down projection over 256-channel pair tiles
   bool down_pair = false;
+  int down_tile = 0;        // token tile of the down kernel (256 with wide tiles while gate/up and `tasks` keep 128)
+  int down_tiles = 0;       // resolved B200MoeShape.down_tiles (0 = not the BF16 tensor-core down kernel)
   // W4A16 kernels: packed-stage ring, operand-stage ring, dynamic shared memory
   int w4_packed_gate_up = 0, w4_operand_gate_up = 0, w4_smem_gate_up = 0;
   int w4_packed_down = 0, w4_operand_down = 0, w4_smem_down = 0;

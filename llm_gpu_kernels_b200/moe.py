@@ -92,7 +92,9 @@ class PreparedMoE:
     kernel_launches: int = 0  # kernels one run() enqueues
     chain: tuple = None       # expert-side plans: (device address, count) of the int32 words the exchange zeroes
     gathers: bool = False     # gate/up gathers token rows through source_rows; grouped_input is empty
-    down_pair: bool = False   # the down projection runs over 256-channel pair tiles (other FP32 summation order over K)
+    down_pair: bool = False   # the down projection runs over 256-channel pair tiles
+    down_tiles: int = 0       # resolved BF16 down schedule: 1 pair, 2 128-channel tiles (two partial sums), 3 wide
+                              # (256-row tiles); pass it as ``down_tiles=`` to a plan that must give the same bits
     source_rows: torch.Tensor = None   # [R] int32: the token behind each grouped row (only when gathers)
     fused_return: bool = False  # expert-side plans: the down projection stores result rows into their owners' buffers
     ep_tables: tuple = None
@@ -225,7 +227,8 @@ def _validate(x, gate_up, down, ids, routing_weights, router_weight, gate_up_sca
 def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None,
              token_tile=0, config=None, warm=True, gate_up_scales=None, down_scales=None,
              route_only_experts=None, valid_routes=None, copy_rows=True, workspace=None,
-             router_bf16_weights=False, residual=None, unchained=False, keep_grouped_input=False, down_pair=None):
+             router_bf16_weights=False, residual=None, unchained=False, keep_grouped_input=False, down_pair=None,
+             down_tiles=None):
     """Validate, allocate the workspace, bind the native plan, run one forward.
 
     With ``gate_up_scales`` / ``down_scales`` the matching weight argument is the packed
@@ -259,7 +262,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
                           route_only=0 if route_only_experts is None else (1 if copy_rows else 2),
                           router_bf16_weights=int(bool(router_bf16_weights)), unchained=int(bool(unchained)),
                           fused_gather=_GATHER[keep_grouped_input],
-                          down_tiles=0 if down_pair is None else (1 if down_pair else 2))
+                          down_tiles=int(down_tiles) if down_tiles is not None
+                          else (0 if down_pair is None else (1 if down_pair else 2)))
     handle = ctypes.c_void_p()
     _native.check(lib.b200moe_plan_create(ctypes.byref(shape), ctypes.byref(handle)))
     try:
@@ -279,7 +283,8 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
             ranks=int32((r,)), scratch=int32((max(1, sizes.scratch // 4),)), router_weight=router_weight,
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
             kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
-            valid_routes=valid_routes, residual=residual, gathers=bool(sizes.gathers), down_pair=bool(sizes.down_pair),
+            valid_routes=valid_routes, residual=residual, gathers=bool(sizes.gathers), down_pair=sizes.down_tiles == 1,
+            down_tiles=sizes.down_tiles,
             source_rows=int32((r,)) if sizes.gathers else None)
         for name, tensor in (workspace or {}).items():  # caller-provided workspace (peer-visible buffers)
             if tuple(tensor.shape) != tuple(getattr(plan, name).shape) or tensor.dtype != getattr(plan, name).dtype:
@@ -319,7 +324,7 @@ def _prepare(x, gate_up, down, ids, routing_weights, *, router_weight=None, sche
 
 
 def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, schedule=None, token_tile=0,
-                router_bf16_weights=False, residual=None, keep_grouped_input=False, down_pair=None):
+                router_bf16_weights=False, residual=None, keep_grouped_input=False, down_pair=None, down_tiles=None):
     """Drop-in for reference ``prepare_moe`` (moe.py:220-245). ``router_bf16_weights`` makes the router round
     its weights through BF16 like the captured model does (scripts/capture_qwen3_moe_layer0.py:587-588).
     ``residual`` ([T,H] bf16, read every forward) is added to the layer result inside the combine kernel:
@@ -327,11 +332,12 @@ def prepare_moe(x, gate_up, down, ids, routing_weights, *, router_weight=None, s
     ``keep_grouped_input=True`` makes every forward fill the ``grouped_input`` workspace tensor as the reference's
     dispatch does; by default the gate/up kernel reads the token rows through ``source_rows`` where that is
     faster (until experts average more than three 128-row tiles); ``"never"`` gathers whenever the kernels can.
-    ``down_pair`` pins the tile schedule of the BF16 down projection (None = shape-only choice); the two schedules
-    sum over K in a different order, so plans that must agree to the bit pin the same one."""
+    ``down_pair`` / ``down_tiles`` pin the tile schedule of the BF16 down projection (None = shape-only choice;
+    ``down_tiles`` 1 = pair tiles, 2 = 128-channel tiles with two partial sums over K, 3 = wide 256-row tiles, as
+    ``PreparedMoE.down_tiles`` reports): plans that must agree to the bit pin the same one."""
     return _prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight, schedule=schedule,
                     token_tile=token_tile, router_bf16_weights=router_bf16_weights, residual=residual,
-                    keep_grouped_input=keep_grouped_input, down_pair=down_pair)
+                    keep_grouped_input=keep_grouped_input, down_pair=down_pair, down_tiles=down_tiles)
 
 
 def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_scales=None, down_scales=None,
@@ -368,7 +374,7 @@ def _prepare_expert_side(gate_up, down, grouped_input, *, token_tile, gate_up_sc
             int32((1,)), GemmConfig(block_m=max(16, sizes.token_tile)),
             schedule=_native.SCHEDULE_NAMES[sizes.schedule], token_tile=sizes.token_tile,
             kernel_launches=sizes.launches, gate_up_scales=gate_up_scales, down_scales=down_scales,
-            down_pair=bool(sizes.down_pair))
+            down_pair=sizes.down_tiles == 1, down_tiles=sizes.down_tiles)
         ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
         buffers = _native.Buffers(
             gate_up=ptr(gate_up), gate_up_scales=ptr(gate_up_scales), down=ptr(down), down_scales=ptr(down_scales),

@@ -45,8 +45,9 @@ def _ranked(base: PreparedMoE) -> PreparedRankedMoE:
 
 def prepare_ranked_moe_launcher(x, gate_up, down, ids, routing_weights, *, router_weight=None,
                                 schedule=None, token_tile=0, router_bf16_weights=False, residual=None,
-                                keep_grouped_input=False, down_pair=None):
+                                keep_grouped_input=False, down_pair=None, down_tiles=None):
     """Drop-in for reference ``prepare_ranked_moe_launcher`` (moe_ranked.py:99-169)."""
     return _ranked(_prepare(x, gate_up, down, ids, routing_weights, router_weight=router_weight,
                             schedule=schedule, token_tile=token_tile, router_bf16_weights=router_bf16_weights,
-                            residual=residual, keep_grouped_input=keep_grouped_input, down_pair=down_pair))
+                            residual=residual, keep_grouped_input=keep_grouped_input, down_pair=down_pair,
+                            down_tiles=down_tiles))

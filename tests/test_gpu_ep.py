@@ -41,7 +41,7 @@ def _run_rank(rank, world, port, shape, result):
         assert m["relative_rms"] <= 5e-3 and m["normalized_max"] <= 8e-3, m
         # parity 2: bit-identical to the single-GPU plan on the same tokens, routes and tile schedule
         expert_plan = ep.backend.expert_plan
-        pinned = dict(token_tile=expert_plan.token_tile, down_pair=expert_plan.down_pair) if expert_plan.schedule == "tcgen05" else {}
+        pinned = dict(token_tile=expert_plan.token_tile, down_tiles=expert_plan.down_tiles) if expert_plan.schedule == "tcgen05" else {}
         single = prepare_ranked_moe_launcher(x[mine].contiguous().to(dev), gate_up.to(dev), down.to(dev),
                                              ids.clone(), rw.clone(), **pinned)
         assert torch.equal(single.run(), out)

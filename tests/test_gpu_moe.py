@@ -133,6 +133,30 @@ def test_down_pair_tiles(dev, t, e, k, h, i, pattern, tile):
     assert m["relative_rms"] <= REL_RMS_BF16, m
 
 
+@pytest.mark.parametrize("t,e,k,h,i,pattern", [(129, 16, 4, 320, 136, "hot"), (300, 4, 2, 256, 128, "all_hot"),
+                                               (700, 8, 2, 192, 200, "random"), (64, 8, 2, 256, 128, "random")])
+@pytest.mark.parametrize("keep", [False, True])
+def test_down_wide_tiles(dev, t, e, k, h, i, pattern, keep):
+    """down_tiles = 3: gate/up and the `tasks` prefix keep token tile 128, the down kernel re-tiles every expert at
+    256 rows from the counts (experts of 600 rows = 256 + 256 + 88, of 30 rows, of none)."""
+    cpu = make_inputs(t, e, k, h, i, pattern=pattern, seed=300 + t, wscale=0.1, signed=True)
+    gpu = tuple(a.to(dev) for a in cpu)
+    p = prep()(*gpu, schedule="tcgen05", token_tile=128, down_tiles=3, keep_grouped_input=keep)
+    assert p.base.down_tiles == 3 and not p.base.down_pair and p.base.token_tile == 128
+    out = p.run()
+    torch.cuda.synchronize()
+    p.check_inputs()
+    check_dispatch(p.base, cpu[0], cpu[3], e)
+    check_output(out, cpu)
+    assert torch.equal(p.run(), out)
+    pair = prep()(*gpu, schedule="tcgen05", token_tile=128, down_tiles=1, keep_grouped_input=keep)
+    assert pair.base.down_tiles == 1
+    m = O.error_metrics(out.float().cpu(), pair.run().float().cpu())
+    assert m["relative_rms"] <= REL_RMS_BF16, m
+    with pytest.raises(ValueError):
+        prep()(*gpu, schedule="tcgen05", token_tile=64, down_tiles=3)
+
+
 @pytest.mark.parametrize("tokens", [17, 193, 1024])
 def test_qwen_shape_full_layer(dev, tokens):
     """benchmark configuration 2: router + experts, Qwen3-30B-A3B layer shape, seeded synthetic weights."""
