@@ -47,7 +47,6 @@ constexpr int kThreads = 192 + kConverters + 64;       // + words TMA, MMA, 4 ep
 constexpr int kMmaWarpB = 6 + kConverters / 32 + 1;
 constexpr int kMaxWords = 6, kMaxOperand = 4;
 constexpr int kWordsK = 256;                           // K covered by one words stage: 128 bytes per channel
-constexpr uint32_t kWTileBytes = kTileM * kBlockK * 2;   // one BF16 weight tile of 64 K: 16 KB
 constexpr uint32_t kWordsTileBytes = kTileM * kWordsK / 2;  // one packed tile of 256 K: 16 KB
 constexpr int kCtrlBytes = 4096;
 
