@@ -246,10 +246,12 @@ int router_ksplit(int hidden, int tokens) {
   const int num_kb = (hidden + kBlockK - 1) / kBlockK;
   int split = 1;
   while (split < 8 && num_kb / (split * 2) >= 2) split *= 2;  // at least two k-blocks per CTA
-  // Only about 16 clusters of 8 CTAs (one CTA per SM) are resident at a time: beyond that the router ran in
-  // waves (13 us at 8 token tiles, 27 us at 17). Smaller clusters keep all token tiles in one wave.
+  // All clusters should be resident at once, or the router runs in waves. Clusters of 8 (one CTA per SM) fit about
+  // two per GPC: 12 of them measured fine (21.5 us at 12 token tiles), 16 did not (35.8 us at 16 token tiles against
+  // 27.6 us with clusters of 4); smaller clusters pack up to 128 CTAs (25.6 us at 32 tiles x 4, 37.9 us at 64 x 2;
+  // 35.7 / 54.3 us when capped at 64 CTAs).
   const int tiles = (tokens + kTileTokens - 1) / kTileTokens;
-  while (split > 1 && tiles * split > 128) split /= 2;
+  while (split > 1 && tiles * split > (split == 8 ? 96 : 128)) split /= 2;
   return split;
 }
 
