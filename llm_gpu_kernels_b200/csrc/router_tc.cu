@@ -41,7 +41,9 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
-template <typename IdT>
+// kPerLane: experts per lane in the routing epilogue (ceil(E / 32) rounded up to 1, 2, 4 or 8): the top-k rounds
+// walk exactly the keys a lane holds.
+template <typename IdT, int kPerLane>
 __global__ void __launch_bounds__(kThreads, 1)
 router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_wr,
                  IdT* __restrict__ ids, float* __restrict__ rw, int* __restrict__ status, int T, int E, int H,
@@ -153,20 +155,19 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     // ---------------------------------------------------------------- rows of this CTA: reduce over the cluster, route
     const int rows_live = min(kTileTokens, T - t0);
     const int rows_per_cta = kTileTokens / ksplit;
-    const int per_lane = e_pad / 32 + ((e_pad % 32) ? 1 : 0);   // <= 8 experts per lane
     const uint32_t logits_addr = smem_u32(logits);
     for (int rr = warp - 2; rr < rows_per_cta; rr += kRowWarps) {
       const int r = static_cast<int>(cta_rank) * rows_per_cta + rr;
       if (r >= rows_live) break;
       {
         // key(x): unsigned, monotonic in x; 0 is below every finite logit and marks "absent / taken"
-        uint32_t key[8];
+        uint32_t key[kPerLane];
         uint32_t kmax_local = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
           const int e = j * 32 + lane;
           uint32_t u = 0;
-          if (j < per_lane && e < E) {
+          if (e < E) {
             float sum_parts = 0.0f;
             for (int sidx = 0; sidx < ksplit; ++sidx) {  // fixed order: slice 0, 1, ...
               uint32_t remote;
@@ -186,7 +187,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         const float m = __uint_as_float((kmax >> 31) ? (kmax ^ 0x80000000u) : ~kmax);
         float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
           if (key[j]) {
             const uint32_t u = key[j];
             sum += expf(__uint_as_float((u >> 31) ? (u ^ 0x80000000u) : ~u) - m);
@@ -199,17 +200,17 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         for (int k = 0; k < K; ++k) {
           uint32_t best = 0;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) best = max(best, key[j]);
+          for (int j = 0; j < kPerLane; ++j) best = max(best, key[j]);
           const uint32_t top = __reduce_max_sync(0xffffffffu, best);
           int cand = 0x7fffffff;                     // lowest expert index holding the top key
 #pragma unroll
-          for (int j = 7; j >= 0; --j)
+          for (int j = kPerLane - 1; j >= 0; --j)
             if (key[j] == top) cand = j * 32 + lane;
           int be = __reduce_min_sync(0xffffffffu, top ? cand : 0x7fffffff);
           if (be >= E) be = min(k, E - 1);           // row exhausted (NaNs / K > finite entries): stay in range
           const int taken = (be & 31) == lane ? (be >> 5) : -1;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) key[j] = j == taken ? 0u : key[j];
+          for (int j = 0; j < kPerLane; ++j) key[j] = j == taken ? 0u : key[j];
           if (lane == k) { my_key = top; my_e = be; }
         }
         float p = 0.0f;
@@ -268,12 +269,19 @@ int configure_router_tc(B200MoePlan& p) {
   p.router_stages = stages;
   p.router_smem = kCtrlBytes + 1024 + stages * stage;
   p.router_ksplit = ksplit;
-  cudaError_t e = cudaFuncSetAttribute(router_tc_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(router_tc_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-  if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(router shared memory) failed: %s", cudaGetErrorString(e));
-    return B200MOE_ERR_CUDA;
+  const void* kernels[] = {
+      reinterpret_cast<const void*>(router_tc_kernel<int, 1>), reinterpret_cast<const void*>(router_tc_kernel<int, 2>),
+      reinterpret_cast<const void*>(router_tc_kernel<int, 4>), reinterpret_cast<const void*>(router_tc_kernel<int, 8>),
+      reinterpret_cast<const void*>(router_tc_kernel<long long, 1>),
+      reinterpret_cast<const void*>(router_tc_kernel<long long, 2>),
+      reinterpret_cast<const void*>(router_tc_kernel<long long, 4>),
+      reinterpret_cast<const void*>(router_tc_kernel<long long, 8>)};
+  for (const void* kernel : kernels) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(router shared memory) failed: %s", cudaGetErrorString(e));
+      return B200MOE_ERR_CUDA;
+    }
   }
   return B200MOE_OK;
 }
@@ -298,9 +306,15 @@ cudaError_t launch_router_typed(const B200MoePlan& p, cudaStream_t s, IdT* ids) 
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   int* status = static_cast<int*>(p.buf.scratch) + router_flag_index(p);  // folded into status by the dispatch
-  return cudaLaunchKernelEx(&cfg, router_tc_kernel<IdT>, p.tm_x, p.tm_router_w, ids,
-                            static_cast<float*>(p.buf.routing_weights), status, sh.tokens, sh.experts, sh.hidden,
-                            sh.topk, e_pad, p.router_stages, p.router_ksplit, sh.router_bf16_weights);
+  auto* rw = static_cast<float*>(p.buf.routing_weights);
+  auto launch = [&](auto kernel) {
+    return cudaLaunchKernelEx(&cfg, kernel, p.tm_x, p.tm_router_w, ids, rw, status, sh.tokens, sh.experts, sh.hidden,
+                              sh.topk, e_pad, p.router_stages, p.router_ksplit, sh.router_bf16_weights);
+  };
+  if (e_pad <= 32) return launch(router_tc_kernel<IdT, 1>);
+  if (e_pad <= 64) return launch(router_tc_kernel<IdT, 2>);
+  if (e_pad <= 128) return launch(router_tc_kernel<IdT, 4>);
+  return launch(router_tc_kernel<IdT, 8>);
 }
 
 
