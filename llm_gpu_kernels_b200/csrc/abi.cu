@@ -224,6 +224,11 @@ int b200moe_plan_create(const B200MoeShape* shape, B200MoePlan** out) {
   p->chain_words = 1 + s.experts;
   // Down projection over pair tiles once an expert averages more than one token tile (shape-only): below that every
   // weight tile is fetched once anyway and the finer 128-channel tiles balance the SMs better.
+  if (s.fused_gather < 0 || s.fused_gather > 2) {
+    delete p;
+    set_error("fused_gather must be 0 (materialise grouped_input), 1 (gather where it is faster) or 2 (wherever possible)");
+    return B200MOE_ERR_INVALID;
+  }
   if (s.down_tiles < 0 || s.down_tiles > 3) {
     delete p;
     set_error("down_tiles must be 0 (shape-only choice), 1 (pair tiles), 2 (128-channel tiles) or 3 (wide tiles)");

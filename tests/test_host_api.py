@@ -71,6 +71,52 @@ def test_plan_create_rejects(kw):
         _native.check(code)
 
 
+def resolved(**kw):
+    lib, code, handle = make_plan(**kw)
+    assert code == 0, _native.last_error()
+    ws = _native.Workspace()
+    assert lib.b200moe_plan_workspace(handle, ctypes.byref(ws)) == 0
+    out = {name: getattr(ws, name) for name, _ in _native.Workspace._fields_ if name != "reserved"}
+    lib.b200moe_plan_destroy(handle)
+    return out
+
+
+def test_gather_rule_is_shape_only():
+    """fused_gather = 1 gathers while experts average at most three 128-row tiles (routes <= 384 x experts); 2 always;
+    0 never. A gathering plan has no grouped_input and a source_rows table instead."""
+    for tokens, expect in ((17, 1), (1024, 1), (6144, 1), (6145, 0), (8192, 0)):
+        ws = resolved(tokens=tokens, fused_gather=1)
+        assert ws["gathers"] == expect, tokens
+        assert ws["grouped_input"] == (0 if expect else tokens * 8 * 2048 * 2)
+        assert ws["source_rows"] == (tokens * 8 * 4 if expect else 0)
+    assert resolved(tokens=8192, fused_gather=2)["gathers"] == 1
+    assert resolved(tokens=1024, fused_gather=0)["gathers"] == 0
+    assert resolved(tokens=1024)["gathers"] == 0                      # the C default of the field is 0
+    assert make_plan(fused_gather=3)[1] == _native.ERR_INVALID
+
+
+def test_down_schedule_resolution():
+    """down_tiles: 0 resolves to pair tiles up to token tile 128 and to one 128-channel tile at 256; 3 (wide) needs
+    token tile 128; W4 and generic plans report 0."""
+    assert resolved(tokens=17)["down_tiles"] == 1 and resolved(tokens=8192)["down_tiles"] == 1
+    assert resolved(tokens=16384)["token_tile"] == 256 and resolved(tokens=16384)["down_tiles"] == 2
+    assert resolved(tokens=1024, down_tiles=2)["down_tiles"] == 2
+    assert resolved(tokens=1024, down_tiles=3)["down_tiles"] == 3
+    assert resolved(tokens=17, token_tile=128, down_tiles=3)["down_tiles"] == 3
+    assert make_plan(tokens=17, down_tiles=3)[1] == _native.ERR_INVALID          # token tile 16
+    assert make_plan(tokens=16384, down_tiles=3)[1] == _native.ERR_INVALID       # token tile 256
+    assert make_plan(down_tiles=4)[1] == _native.ERR_INVALID
+    assert resolved(down_format=_native.WEIGHTS_W4G128, gate_up_format=_native.WEIGHTS_W4G128)["down_tiles"] == 0
+    assert resolved(hidden=67, intermediate=33, experts=3, topk=2, tokens=9)["down_tiles"] == 0
+
+
+@pytest.mark.parametrize("tokens,launches", [(17, 5), (256, 5), (257, 5), (1024, 5), (2048, 5), (2049, 7), (8192, 7)])
+def test_launches_per_forward(tokens, launches):
+    """Router + dispatch + gate/up + down + combine: the dispatch is one kernel up to 16384 routes (a cluster of 1, 2,
+    4 or 8 blocks) when no rows are copied, three kernels above."""
+    assert resolved(tokens=tokens, use_router=1, fused_gather=1)["launches"] == launches
+
+
 def test_odd_shapes_take_the_generic_schedule():
     lib, code, handle = make_plan(hidden=67, intermediate=33, experts=3, topk=2, tokens=9)
     assert code == 0
